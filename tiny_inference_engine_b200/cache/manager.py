@@ -2,7 +2,9 @@
 
 Layers are put into groups by what they need of the cache (kv heads, head size, all keys or a
 window of them). Each group has its own page pool and its own storage
-`[planes][2 (K, V)][pages][kv_heads][page_size][head_dim]`, one plane per run entry of the
+`[planes][2 (K, V)][pages][kv_heads][page_size][head_dim]` (where value heads have a size of their
+own: keys `[planes][pages][kv_heads][page_size][head_dim]` and values likewise with `value_dim`,
+one after the other in one buffer), one plane per run entry of the
 group; within a group a page id addresses the same token slots in every plane, as in the
 reference's single group (src/kv/paged_kv_cache.h:27-30). A request holds one block table
 per group: token j lives in page table[j // page_size] at offset j % page_size
@@ -78,6 +80,7 @@ class GroupSpec:
     head_dim: int
     window: int
     entries: tuple[int, ...]   # run entries whose planes live in this group
+    value_dim: int = 0         # size of a value head; 0: head_dim
 
 
 class CacheManager:
@@ -98,16 +101,18 @@ class CacheManager:
         for i, need in enumerate(needs):
             if need is None:
                 continue
-            if need.kv_heads <= 0 or need.head_dim <= 0 or need.kind not in ("full", "window") or \
+            value_dim = getattr(need, "value_dim", 0)
+            if need.kv_heads <= 0 or need.head_dim <= 0 or value_dim < 0 or need.kind not in ("full", "window") or \
                     (need.kind == "window" and need.window <= 0):
                 raise InvalidArgument(f"bad cache need of run entry {i}: {need}")
-            keyed.setdefault((need.kind, need.kv_heads, need.head_dim, need.window if need.kind == "window" else 0),
-                             []).append(i)
-        self.groups = [GroupSpec(k[0], k[1], k[2], k[3], tuple(v)) for k, v in keyed.items()]
+            keyed.setdefault((need.kind, need.kv_heads, need.head_dim, need.window if need.kind == "window" else 0,
+                              0 if value_dim == need.head_dim else value_dim), []).append(i)
+        self.groups = [GroupSpec(k[0], k[1], k[2], k[3], tuple(v), k[4]) for k, v in keyed.items()]
         self._entry_group = {e: gi for gi, g in enumerate(self.groups) for e in g.entries}
         self._entry_plane = {e: pi for g in self.groups for pi, e in enumerate(g.entries)}
         elem = 4 if dtype is None else _elem_size(dtype)
-        group_bytes = [2 * len(g.entries) * g.kv_heads * page_size * g.head_dim * elem for g in self.groups]
+        group_bytes = [len(g.entries) * g.kv_heads * page_size * (g.head_dim + (g.value_dim or g.head_dim)) * elem
+                       for g in self.groups]
         # what a window group can ever use (None: as many pages as the other groups)
         bounded = [None] * len(self.groups)
         if window_requests is not None:
@@ -137,8 +142,12 @@ class CacheManager:
         if device is not None:
             import torch
             for g, n in zip(self.groups, self.group_pages):
-                self.storage.append(torch.zeros((len(g.entries), 2, n, g.kv_heads, page_size, g.head_dim),
-                                                dtype=dtype, device=device))
+                if g.value_dim:      # keys of every plane, then values of every plane, in one flat buffer
+                    rows = len(g.entries) * n * g.kv_heads * page_size
+                    self.storage.append(torch.zeros(rows * (g.head_dim + g.value_dim), dtype=dtype, device=device))
+                else:
+                    self.storage.append(torch.zeros((len(g.entries), 2, n, g.kv_heads, page_size, g.head_dim),
+                                                    dtype=dtype, device=device))
         self.state_slots = state_slots
         self._live: set[int] = set()
 
@@ -285,6 +294,13 @@ class CacheManager:
             return LayerCache(None, None, -1, False)
         gi, pi = self._entry_group[entry], self._entry_plane[entry]
         st = self.storage[gi]
+        g = self.groups[gi]
+        if g.value_dim:
+            n, planes = self.group_pages[gi], len(g.entries)
+            rows = n * g.kv_heads * self.page_size
+            keys = st[:planes * rows * g.head_dim].view(planes, n, g.kv_heads, self.page_size, g.head_dim)
+            values = st[planes * rows * g.head_dim:].view(planes, n, g.kv_heads, self.page_size, g.value_dim)
+            return LayerCache(keys[pi], values[pi], gi, writes)
         return LayerCache(st[pi, 0], st[pi, 1], gi, writes)
 
     def max_tokens_per_request(self) -> int:

@@ -16,6 +16,9 @@ class Architecture:
     parse_config: Callable[[dict], Any]      # config.json (dict) -> typed configuration
     build_spec: Callable[[Any], ModelSpec]   # typed configuration -> ModelSpec
     model_types: tuple[str, ...] = ()        # config.json "model_type" values that also select it
+    # Sizes that config.json does not give and the checkpoint's tensor shapes do: {tensor name: shape} -> a value
+    # that `parse_config(config_json, value)` takes as its second argument. None: the configuration says it all.
+    shapes_to_config: Callable[[dict], Any] | None = None
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
@@ -32,9 +35,11 @@ def architectures() -> list[str]:
 
 
 def resolve_architecture(config_json: dict) -> Architecture:
-    """Chooses by `architectures[0]`, else by `model_type` (the only key the reference reads,
-    src/model/config.cpp:39-42)."""
+    """Chooses by `architectures[0]` (or the single name under `architecture`), else by `model_type` (the only
+    key the reference reads, src/model/config.cpp:39-42)."""
     names = config_json.get("architectures") or []
+    if not names and isinstance(config_json.get("architecture"), str):
+        names = [config_json["architecture"]]
     if names:
         if names[0] in _ARCHITECTURES:
             return _ARCHITECTURES[names[0]]
@@ -64,11 +69,21 @@ def read_config_json(model_dir) -> dict:
     return cfg
 
 
+def checkpoint_present(model_dir) -> bool:
+    d = Path(model_dir)
+    return (d / "model.safetensors").exists() or (d / "model.safetensors.index.json").exists()
+
+
 def load_config(model_dir):
     """config.json of a folder -> (architecture, typed configuration, model description)."""
     raw = read_config_json(model_dir)
     arch = resolve_architecture(raw)
-    cfg = arch.parse_config(raw)
+    if arch.shapes_to_config is not None and checkpoint_present(model_dir):
+        from ..weights.loader import SafetensorsSource
+        shapes = {n: tuple(s) for n, (s, _) in SafetensorsSource(model_dir).shapes().items()}
+        cfg = arch.parse_config(raw, arch.shapes_to_config(shapes))
+    else:
+        cfg = arch.parse_config(raw)
     spec = arch.build_spec(cfg)
     spec.validate()
     return arch, cfg, spec

@@ -25,14 +25,18 @@ class PartSpec:
 class LayerSpec:
     """One layer: a sequence mixer and a feed-forward, each behind its own norm, arranged by `block`.
 
-    `prefix` is the checkpoint name prefix of the layer (for instance "model.layers.3.").
+    `prefix` is the checkpoint name prefix of the layer (for instance "model.layers.3."). A layer
+    without a feed-forward has `ffn` and `ffn_norm` None; arrangements that norm a sublayer's output
+    before adding it name those norms in `mixer_post_norm` and `ffn_post_norm`.
     """
     prefix: str
     block: PartSpec
     mixer: PartSpec
     mixer_norm: PartSpec
-    ffn: PartSpec
-    ffn_norm: PartSpec
+    ffn: PartSpec | None
+    ffn_norm: PartSpec | None
+    mixer_post_norm: PartSpec | None = None
+    ffn_post_norm: PartSpec | None = None
 
 
 @dataclass(frozen=True)

@@ -38,6 +38,7 @@ struct AttnArgs {
   int q_heads, kv_heads, head_dim, page_size;
   int window;               // 0 = all keys
   float scale;
+  int v_dim;                // size of a value head (and of an output head); keys and queries have head_dim
 };
 
 // One warp: online softmax over keys [lo, hi] of one (query vector, kv head).
@@ -46,15 +47,15 @@ struct AttnArgs {
 template <typename T, int DPL>
 __device__ __forceinline__ void attend_range(const float* __restrict__ qs, const T* __restrict__ kc,
                                              const T* __restrict__ vc, const int* __restrict__ table, int kvh,
-                                             int kv_heads, int head_dim, int page_size, float scale, int lo, int hi,
-                                             float& m, float& l, float (&acc)[DPL]) {
+                                             int kv_heads, int head_dim, int v_dim, int page_size, float scale, int lo,
+                                             int hi, float& m, float& l, float (&acc)[DPL]) {
   constexpr int V = Vec16<T>::N;
   const int lane = threadIdx.x & 31;
   const int d0 = lane * DPL;
   for (int base = lo; base <= hi; base += 32) {
     const int j = base + lane;
     const bool valid = j <= hi;
-    int row = 0;  // index of the key's row in units of head_dim elements
+    int row = 0;  // index of the key's row: head_dim elements in the key plane, v_dim in the value plane
     float s = -INFINITY;
     if (valid) {
       const int page = table[j / page_size];
@@ -80,8 +81,8 @@ __device__ __forceinline__ void attend_range(const float* __restrict__ qs, const
     for (int jj = 0; jj < count; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const int rj = __shfl_sync(0xffffffffu, row, jj);
-      if (d0 < head_dim) {
-        const T* vr = vc + static_cast<long long>(rj) * head_dim + d0;
+      if (d0 < v_dim) {
+        const T* vr = vc + static_cast<long long>(rj) * v_dim + d0;
 #pragma unroll
         for (int e = 0; e < DPL; ++e) acc[e] = fmaf(pj, ld(vr + e), acc[e]);
       }
@@ -112,10 +113,10 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnArgs a) {
   float m = -INFINITY, l = 0.0f, acc[DPL] = {};
   attend_range<T, DPL>(qs, static_cast<const T*>(a.k_cache), static_cast<const T*>(a.v_cache),
                        a.block_tables + static_cast<long long>(s) * a.max_blocks, kvh, a.kv_heads, a.head_dim,
-                       a.page_size, a.scale, lo, pos, m, l, acc);
+                       a.v_dim, a.page_size, a.scale, lo, pos, m, l, acc);
   const int d0 = lane * DPL;
-  if (d0 < a.head_dim) {
-    T* o = static_cast<T*>(a.out) + (static_cast<long long>(t) * a.q_heads + h) * a.head_dim + d0;
+  if (d0 < a.v_dim) {
+    T* o = static_cast<T*>(a.out) + (static_cast<long long>(t) * a.q_heads + h) * a.v_dim + d0;
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;  // no keys (a padding row): zeros
 #pragma unroll
     for (int e = 0; e < DPL; ++e) st(o + e, acc[e] * inv);
@@ -123,7 +124,7 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnArgs a) {
 }
 
 // Split kernel: sequences listed in `seq_list` (each brings exactly one query row).
-// scratch: [n_list, q_heads, max_splits, head_dim + 2] floats (acc, then m, l).
+// scratch: [n_list, q_heads, max_splits, v_dim + 2] floats (acc, then m, l).
 template <typename T, int DPL>
 __global__ void __launch_bounds__(128) attention_split_kernel(AttnArgs a, const int* __restrict__ seq_list, int n_list,
                                                               int split_keys, int max_splits, float* __restrict__ scratch) {
@@ -154,16 +155,16 @@ __global__ void __launch_bounds__(128) attention_split_kernel(AttnArgs a, const 
   float m = -INFINITY, l = 0.0f, acc[DPL] = {};
   attend_range<T, DPL>(qs, static_cast<const T*>(a.k_cache), static_cast<const T*>(a.v_cache),
                        a.block_tables + static_cast<long long>(s) * a.max_blocks, kvh, a.kv_heads, a.head_dim,
-                       a.page_size, a.scale, lo, hi, m, l, acc);
-  float* dst = scratch + ((static_cast<long long>(li) * a.q_heads + h) * max_splits + split) * (a.head_dim + 2);
+                       a.v_dim, a.page_size, a.scale, lo, hi, m, l, acc);
+  float* dst = scratch + ((static_cast<long long>(li) * a.q_heads + h) * max_splits + split) * (a.v_dim + 2);
   const int d0 = lane * DPL;
-  if (d0 < a.head_dim) {
+  if (d0 < a.v_dim) {
 #pragma unroll
     for (int e = 0; e < DPL; ++e) dst[d0 + e] = acc[e];
   }
   if (lane == 0) {
-    dst[a.head_dim] = m;
-    dst[a.head_dim + 1] = l;
+    dst[a.v_dim] = m;
+    dst[a.v_dim + 1] = l;
   }
 }
 
@@ -221,7 +222,9 @@ int launch_attention(const AttnArgs& a, const int* row_seq_unused, const int* se
   (void)row_seq_unused;
   const int warps = 4;
   const size_t smem = static_cast<size_t>(warps) * a.head_dim * sizeof(float);
-  const int dpl = (a.head_dim + 31) / 32;
+  AttnArgs merge_args = a;            // the merge kernel sees output heads only
+  merge_args.head_dim = a.v_dim;
+  const int dpl = (a.v_dim + 31) / 32;
 #define TIE_ATTN_CASE(D)                                                                                         \
   do {                                                                                                           \
     if (rows_kernel) {                                                                                           \
@@ -232,7 +235,7 @@ int launch_attention(const AttnArgs& a, const int* row_seq_unused, const int* se
       if (items > 0) {                                                                                           \
         TIE_LAUNCH((attention_split_kernel<T, D>), dim3(ceil_div(items, warps), max_splits), warps * 32, smem, s,           \
             a, seq_list, n_list, split_keys, max_splits, scratch);                                               \
-        TIE_LAUNCH((attention_merge_kernel<T>), static_cast<int>(items), kMergeThreads, 0, s, a, seq_list, n_list, split_keys, \
+        TIE_LAUNCH((attention_merge_kernel<T>), static_cast<int>(items), kMergeThreads, 0, s, merge_args, seq_list, n_list, split_keys, \
                                                                                     max_splits, scratch);         \
       }                                                                                                          \
     }                                                                                                            \
@@ -257,6 +260,7 @@ static int check_attn(const AttnArgs& a) {
               "attention: head_dim %d must be a multiple of 8 and at most 512", a.head_dim);
   TIE_REQUIRE(a.head_dim <= 256 || a.head_dim % 16 == 0, "attention: head_dim %d above 256 must be a multiple of 16",
               a.head_dim);
+  TIE_REQUIRE(a.v_dim > 0 && a.v_dim <= 512, "attention: value heads of %d (1 to 512)", a.v_dim);
   TIE_REQUIRE(a.page_size > 0 && a.max_blocks > 0, "attention: bad page geometry");
   TIE_REQUIRE(a.window >= 0, "attention: negative window");
   return kOk;
@@ -269,7 +273,7 @@ TIE_API int tie_attention_rows(int dtype, const void* q, long long q_stride, con
                                const int* block_tables, int max_blocks, int rows, int seqs, int q_heads, int kv_heads,
                                int head_dim, int page_size, int window, float scale, cudaStream_t s) {
   const AttnArgs a{q, k_cache, v_cache, out, seq_of_row, query_start, context_lens, block_tables, q_stride, max_blocks,
-                   rows, seqs, q_heads, kv_heads, head_dim, page_size, window, scale};
+                   rows, seqs, q_heads, kv_heads, head_dim, page_size, window, scale, head_dim};
   if (const int st = check_attn(a)) return st;
   if (dtype == TIE_F32) return launch_attention<float>(a, nullptr, nullptr, 0, 0, 0, nullptr, 1, s);
   if (dtype == TIE_BF16) return launch_attention<__nv_bfloat16>(a, nullptr, nullptr, 0, 0, 0, nullptr, 1, s);
@@ -285,7 +289,7 @@ TIE_API int tie_attention_split(int dtype, const void* q, long long q_stride, co
                                 int window, float scale, const int* seq_list, int n_list, int split_keys,
                                 int max_splits, float* scratch, cudaStream_t s) {
   const AttnArgs a{q, k_cache, v_cache, out, nullptr, query_start, context_lens, block_tables, q_stride, max_blocks,
-                   0, seqs, q_heads, kv_heads, head_dim, page_size, window, scale};
+                   0, seqs, q_heads, kv_heads, head_dim, page_size, window, scale, head_dim};
   if (const int st = check_attn(a)) return st;
   TIE_REQUIRE(split_keys > 0 && max_splits > 0 && max_splits <= kMergeMaxSplits && scratch != nullptr,
               "attention split: bad split geometry (at most %d splits)", kMergeMaxSplits);
@@ -323,6 +327,38 @@ TIE_API int tie_attention_merge(int dtype, void* out, const int* query_start, co
   TIE_RETURN_LAUNCH("attention_merge");
 }
 
+// The same two for keys and values of different head sizes: queries and keys have head_dim, values and the
+// output v_dim (planes [pages, kv_heads, page_size, head_dim] and [pages, kv_heads, page_size, v_dim]).
+TIE_API int tie_attention_rows_dv(int dtype, const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                                  void* out, const int* seq_of_row, const int* query_start, const int* context_lens,
+                                  const int* block_tables, int max_blocks, int rows, int seqs, int q_heads, int kv_heads,
+                                  int head_dim, int v_dim, int page_size, int window, float scale, cudaStream_t s) {
+  const AttnArgs a{q, k_cache, v_cache, out, seq_of_row, query_start, context_lens, block_tables, q_stride, max_blocks,
+                   rows, seqs, q_heads, kv_heads, head_dim, page_size, window, scale, v_dim};
+  if (const int st = check_attn(a)) return st;
+  if (dtype == TIE_F32) return launch_attention<float>(a, nullptr, nullptr, 0, 0, 0, nullptr, 1, s);
+  if (dtype == TIE_BF16) return launch_attention<__nv_bfloat16>(a, nullptr, nullptr, 0, 0, 0, nullptr, 1, s);
+  set_error("attention: unknown dtype code %d", dtype);
+  return kBadArgument;
+}
+
+TIE_API int tie_attention_split_dv(int dtype, const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                                   void* out, const int* query_start, const int* context_lens, const int* block_tables,
+                                   int max_blocks, int seqs, int q_heads, int kv_heads, int head_dim, int v_dim,
+                                   int page_size, int window, float scale, const int* seq_list, int n_list, int split_keys,
+                                   int max_splits, float* scratch, cudaStream_t s) {
+  const AttnArgs a{q, k_cache, v_cache, out, nullptr, query_start, context_lens, block_tables, q_stride, max_blocks,
+                   0, seqs, q_heads, kv_heads, head_dim, page_size, window, scale, v_dim};
+  if (const int st = check_attn(a)) return st;
+  TIE_REQUIRE(split_keys > 0 && max_splits > 0 && max_splits <= kMergeMaxSplits && scratch != nullptr,
+              "attention split: bad split geometry (at most %d splits)", kMergeMaxSplits);
+  if (dtype == TIE_F32) return launch_attention<float>(a, nullptr, seq_list, n_list, split_keys, max_splits, scratch, 0, s);
+  if (dtype == TIE_BF16)
+    return launch_attention<__nv_bfloat16>(a, nullptr, seq_list, n_list, split_keys, max_splits, scratch, 0, s);
+  set_error("attention: unknown dtype code %d", dtype);
+  return kBadArgument;
+}
+
 // ---------------------------------------------------------------------------------------------
 // The variant of tie_attention_split that allocates nothing (see attention_noalloc.h).
 #include "attention_noalloc.h"
@@ -342,7 +378,7 @@ TIE_API int tie_attention_split_noalloc(int dtype, const void* q, long long q_st
                                         int head_dim, int page_size, int window, float scale, const int* seq_list,
                                         int n_list, int split_keys, int max_splits, cudaStream_t s) {
   const AttnArgs a{q, k_cache, v_cache, out, nullptr, query_start, context_lens, block_tables, q_stride, max_blocks,
-                   0, seqs, q_heads, kv_heads, head_dim, page_size, window, scale};
+                   0, seqs, q_heads, kv_heads, head_dim, page_size, window, scale, head_dim};
   if (const int st = check_attn(a)) return st;
   TIE_REQUIRE(n_list >= 0 && split_keys > 0 && max_splits > 0 && max_splits <= kMergeMaxSplits,
               "attention split (no alloc): bad split geometry (at most %d splits)", kMergeMaxSplits);

@@ -1,0 +1,306 @@
+// The gated delta rule with one decay per key channel, as a recurrence over the tokens of each sequence.
+//
+// Per value head, a float matrix S (key channels x value channels) is carried from token to token:
+//
+//     S <- diag(decay_t) S;   u = beta_t (v_t - S^T k_t);   S <- S + k_t u^T;   o_t = S^T q_t
+//
+// (the read-out sees the token's own write). q_t and k_t are unit vectors per head (q also scaled), made from
+// projections that pass a short causal convolution over time and SiLU; decay_t = exp(-rate_h softplus(a_t + bias))
+// per key channel. Columns of S do not depend on one another, so the work is cut by (sequence, head, columns).
+//
+// Three kernels, all of them float inside:
+//   delta_prep   one block per token: convolution (its first taps - 1 inputs come from the sequence's state slot or
+//                from the rows ahead of it in the step) + SiLU, unit norm of q and k per head, sigmoid of beta.
+//   delta_rule   one block per (sequence, head, 16 columns): the recurrence over the sequence's tokens of the
+//                step, state read from and written back to the slot. Eight lanes share a column, each holding
+//                every eighth key channel; decays are worked out while a chunk of tokens is staged in shared
+//                memory. The block of head 0, columns 0 also moves the convolution's last inputs into the slot.
+//   delta_out    one warp per (token, head): o / rms(o) * w * sigmoid(gate).
+//
+// A state slot is one float row: S of every head [heads, dim, vdim], then the convolution's last taps - 1
+// inputs [taps - 1, channels] (oldest first), channels = q, k, v one after the other.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace tie {
+
+struct DeltaShape {
+  int heads, kv_heads, dim, vdim, taps;
+  int channels() const { return 2 * kv_heads * dim + heads * vdim; }
+};
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplusf_(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+
+// proj row: q at q_off [kv_heads * dim], k at k_off, v at v_off [heads * vdim], beta at b_off [heads].
+template <typename T>
+__global__ void __launch_bounds__(128) delta_prep_kernel(const T* __restrict__ proj, long long stride, int q_off, int k_off,
+                                                         int v_off, int b_off, const float* __restrict__ conv_w,
+                                                         const float* __restrict__ state, long long state_stride,
+                                                         long long conv_state_off, const int* __restrict__ seq_of_row,
+                                                         const int* __restrict__ query_start,
+                                                         const int* __restrict__ state_slots, DeltaShape sh, float unit_eps,
+                                                         float q_scale, float* __restrict__ qn, float* __restrict__ kn,
+                                                         float* __restrict__ vn, float* __restrict__ beta) {
+  pdl_sync();
+  extern __shared__ float buf[];     // the convolved q and k of this token
+  const int t = blockIdx.x;
+  const int s = seq_of_row[t];
+  const int j = t - query_start[s];          // tokens of this sequence ahead of this one in the step
+  const int slot = state_slots[s];
+  const int nqk = sh.kv_heads * sh.dim, nv = sh.heads * sh.vdim, C = 2 * nqk + nv, taps = sh.taps;
+  const float* tail = slot >= 0 ? state + slot * state_stride + conv_state_off : nullptr;
+  const T* row = proj + static_cast<long long>(t) * stride;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const int col = c < nqk ? q_off + c : (c < 2 * nqk ? k_off + (c - nqk) : v_off + (c - 2 * nqk));
+    float y = 0.0f;
+    for (int i = 0; i < taps; ++i) {
+      const int back = taps - 1 - i;         // this tap's input is `back` tokens ahead of the current one
+      float in;
+      if (back <= j) in = ld(row - static_cast<long long>(back) * stride + col);
+      else in = tail ? tail[static_cast<long long>(j + i) * C + c] : 0.0f;
+      y = fmaf(conv_w[c * taps + i], in, y);
+    }
+    y = y * sigmoidf_(y);
+    if (c < 2 * nqk) buf[c] = y;
+    else vn[static_cast<long long>(t) * nv + (c - 2 * nqk)] = y;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int h = warp; h < 2 * sh.kv_heads; h += warps) {    // q heads, then k heads
+    const float* x = buf + h * sh.dim;
+    float ss = 0.0f;
+    for (int d = lane; d < sh.dim; d += 32) ss += x[d] * x[d];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss + unit_eps);
+    const bool is_q = h < sh.kv_heads;
+    float* dst = (is_q ? qn : kn) + static_cast<long long>(t) * nqk + (is_q ? h : h - sh.kv_heads) * sh.dim;
+    for (int d = lane; d < sh.dim; d += 32) dst[d] = is_q ? (x[d] * inv) * q_scale : x[d] * inv;
+  }
+  for (int h = threadIdx.x; h < sh.heads; h += blockDim.x) beta[static_cast<long long>(t) * sh.heads + h] = sigmoidf_(ld(row + b_off + h));
+}
+
+constexpr int kDeltaLanes = 8;       // lanes that share a column of S
+constexpr int kDeltaCols = 16;       // columns of a block (128 threads)
+
+// RMAX: key channels a lane may hold (dim <= 8 * RMAX).
+template <typename T, int RMAX>
+__global__ void __launch_bounds__(kDeltaLanes * kDeltaCols) delta_rule_kernel(
+    const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vn, const float* __restrict__ beta,
+    const float* __restrict__ a_raw, long long a_stride, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+    float* __restrict__ state, long long state_stride, long long conv_state_off, const T* __restrict__ proj,
+    long long proj_stride, int q_off, int k_off, int v_off, const int* __restrict__ query_start,
+    const int* __restrict__ state_slots, DeltaShape sh, int chunk, float* __restrict__ out) {
+  pdl_sync();
+  extern __shared__ float smem[];
+  const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kDeltaCols;
+  const int slot = state_slots[s];
+  if (slot < 0) return;                       // a sequence that pads a captured batch
+  const int t0 = query_start[s], n = query_start[s + 1] - t0;
+  const int dim = sh.dim, vdim = sh.vdim, nqk = sh.kv_heads * dim, nv = sh.heads * vdim;
+  const int g = h / (sh.heads / sh.kv_heads);
+  const int lane8 = threadIdx.x % kDeltaLanes, col = col0 + threadIdx.x / kDeltaLanes;
+  const bool live = col < vdim;
+  float* S = state + slot * state_stride + static_cast<long long>(h) * dim * vdim;
+  float sreg[RMAX];
+#pragma unroll
+  for (int r = 0; r < RMAX; ++r) {
+    const int rowi = lane8 + kDeltaLanes * r;
+    sreg[r] = (live && rowi < dim) ? S[static_cast<long long>(rowi) * vdim + col] : 0.0f;
+  }
+  float* kb = smem;                           // [chunk][dim]
+  float* qb = kb + chunk * dim;
+  float* gb = qb + chunk * dim;               // decays
+  float* vb = gb + chunk * dim;               // [chunk][kDeltaCols]
+  float* bb = vb + chunk * kDeltaCols;        // [chunk]
+  const float rate = expf(a_log[h]);
+  for (int c0 = 0; c0 < n; c0 += chunk) {
+    const int cn = min(chunk, n - c0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < cn * dim; i += blockDim.x) {
+      const int tc = i / dim, d = i % dim;
+      const long long t = t0 + c0 + tc;
+      kb[i] = kn[t * nqk + g * dim + d];
+      qb[i] = qn[t * nqk + g * dim + d];
+      const float step = softplusf_(a_raw[t * a_stride + h * dim + d] + dt_bias[h * dim + d]);
+      gb[i] = expf(-rate * step);
+    }
+    for (int i = threadIdx.x; i < cn * kDeltaCols; i += blockDim.x) {
+      const int tc = i / kDeltaCols, c = col0 + i % kDeltaCols;
+      vb[i] = c < vdim ? vn[(t0 + c0 + tc) * static_cast<long long>(nv) + h * vdim + c] : 0.0f;
+    }
+    for (int i = threadIdx.x; i < cn; i += blockDim.x) bb[i] = beta[(t0 + c0 + i) * static_cast<long long>(sh.heads) + h];
+    __syncthreads();
+    for (int tc = 0; tc < cn; ++tc) {
+      const float* kt = kb + tc * dim;
+      const float* qt = qb + tc * dim;
+      const float* gt = gb + tc * dim;
+      float dot = 0.0f;
+#pragma unroll
+      for (int r = 0; r < RMAX; ++r) {
+        const int rowi = lane8 + kDeltaLanes * r;
+        if (rowi < dim) {
+          sreg[r] *= gt[rowi];
+          dot = fmaf(kt[rowi], sreg[r], dot);
+        }
+      }
+      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+      const float u = bb[tc] * (vb[tc * kDeltaCols + threadIdx.x / kDeltaLanes] - dot);
+      float o = 0.0f;
+#pragma unroll
+      for (int r = 0; r < RMAX; ++r) {
+        const int rowi = lane8 + kDeltaLanes * r;
+        if (rowi < dim) {
+          sreg[r] = fmaf(kt[rowi], u, sreg[r]);
+          o = fmaf(qt[rowi], sreg[r], o);
+        }
+      }
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      o += __shfl_xor_sync(0xffffffffu, o, 4);
+      if (live && lane8 == 0) out[(t0 + c0 + tc) * static_cast<long long>(nv) + h * vdim + col] = o;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int r = 0; r < RMAX; ++r) {
+      const int rowi = lane8 + kDeltaLanes * r;
+      if (rowi < dim) S[static_cast<long long>(rowi) * vdim + col] = sreg[r];
+    }
+  }
+  // The convolution's last taps - 1 inputs after this step: from the step's rows where it brought enough,
+  // else what the slot held moves up.
+  if (h == 0 && blockIdx.z == 0 && sh.taps > 1) {
+    const int C = 2 * nqk + nv, keep = sh.taps - 1;
+    float* tail = state + slot * state_stride + conv_state_off;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+      const int pc = c < nqk ? q_off + c : (c < 2 * nqk ? k_off + (c - nqk) : v_off + (c - 2 * nqk));
+      for (int i = 0; i < keep; ++i) {
+        const int from = n - keep + i;        // offset in the step of the token that lands at place i
+        tail[static_cast<long long>(i) * C + c] = from >= 0 ? ld(proj + (t0 + from) * proj_stride + pc)
+                                                            : tail[static_cast<long long>(n + i) * C + c];
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) delta_out_kernel(const float* __restrict__ o, const float* __restrict__ gate,
+                                                        long long gate_stride, const float* __restrict__ w, float eps,
+                                                        T* __restrict__ out, int heads, int vdim, long long items) {
+  pdl_sync();
+  const int lane = threadIdx.x & 31;
+  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= items) return;
+  const long long t = item / heads;
+  const int h = static_cast<int>(item % heads);
+  const float* x = o + item * vdim;
+  float ss = 0.0f;
+  for (int d = lane; d < vdim; d += 32) ss += x[d] * x[d];
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / static_cast<float>(vdim) + eps);
+  for (int d = lane; d < vdim; d += 32)
+    st(out + item * vdim + d, ((x[d] * inv) * w[d]) * sigmoidf_(gate[t * gate_stride + h * vdim + d]));
+}
+
+}  // namespace tie
+
+using namespace tie;
+
+static int check_delta(const DeltaShape& sh) {
+  TIE_REQUIRE(sh.heads > 0 && sh.kv_heads > 0 && sh.heads % sh.kv_heads == 0 && sh.dim > 0 && sh.dim <= 256 && sh.vdim > 0 &&
+                  sh.taps >= 1 && sh.taps <= 16,
+              "delta rule: bad shape heads=%d/%d dim=%d (1 to 256) vdim=%d taps=%d (1 to 16)", sh.heads, sh.kv_heads, sh.dim,
+              sh.vdim, sh.taps);
+  return kOk;
+}
+
+TIE_API int tie_delta_prep(int dtype, const void* proj, long long stride, int q_off, int k_off, int v_off, int b_off,
+                           const float* conv_w, const float* state, long long state_stride, long long conv_state_off,
+                           const int* seq_of_row, const int* query_start, const int* state_slots, int tokens, int heads,
+                           int kv_heads, int dim, int vdim, int taps, float unit_eps, float q_scale, float* qn, float* kn,
+                           float* vn, float* beta, cudaStream_t s) {
+  const DeltaShape sh{heads, kv_heads, dim, vdim, taps};
+  if (const int st_ = check_delta(sh)) return st_;
+  if (tokens <= 0) return kOk;
+  const size_t smem = static_cast<size_t>(2) * kv_heads * dim * sizeof(float);
+  TIE_REQUIRE(smem <= 48 * 1024, "delta_prep: q and k of %d values do not fit shared memory", 2 * kv_heads * dim);
+  if (dtype == TIE_F32) {
+    TIE_LAUNCH((delta_prep_kernel<float>), tokens, 128, smem, s, static_cast<const float*>(proj), stride, q_off, k_off, v_off, b_off,
+               conv_w, state, state_stride, conv_state_off, seq_of_row, query_start, state_slots, sh, unit_eps, q_scale, qn, kn,
+               vn, beta);
+  } else if (dtype == TIE_BF16) {
+    TIE_LAUNCH((delta_prep_kernel<__nv_bfloat16>), tokens, 128, smem, s, static_cast<const __nv_bfloat16*>(proj), stride, q_off,
+               k_off, v_off, b_off, conv_w, state, state_stride, conv_state_off, seq_of_row, query_start, state_slots, sh,
+               unit_eps, q_scale, qn, kn, vn, beta);
+  } else {
+    set_error("unknown dtype code %d", dtype);
+    return kBadArgument;
+  }
+  TIE_RETURN_LAUNCH("delta_prep");
+}
+
+template <typename T>
+static int launch_delta_rule(const float* qn, const float* kn, const float* vn, const float* beta, const float* a_raw,
+                             long long a_stride, const float* dt_bias, const float* a_log, float* state,
+                             long long state_stride, long long conv_state_off, const void* proj, long long proj_stride,
+                             int q_off, int k_off, int v_off, const int* query_start, const int* state_slots, int seqs,
+                             const DeltaShape& sh, float* out, cudaStream_t s) {
+  const dim3 grid(seqs, sh.heads, ceil_div(sh.vdim, kDeltaCols));
+  const int per_token = 3 * sh.dim + kDeltaCols + 1;
+  int chunk = (40 * 1024 / static_cast<int>(sizeof(float))) / per_token;
+  chunk = chunk > 32 ? 32 : (chunk < 1 ? 1 : chunk);
+  const size_t smem = static_cast<size_t>(chunk) * per_token * sizeof(float);
+  const T* p = static_cast<const T*>(proj);
+#define TIE_DELTA_CASE(R)                                                                                                  \
+  TIE_LAUNCH((delta_rule_kernel<T, R>), grid, kDeltaLanes * kDeltaCols, smem, s, qn, kn, vn, beta, a_raw, a_stride, dt_bias, a_log, \
+             state, state_stride, conv_state_off, p, proj_stride, q_off, k_off, v_off, query_start, state_slots, sh, chunk, out)
+  const int r = (sh.dim + kDeltaLanes - 1) / kDeltaLanes;
+  if (r <= 2) TIE_DELTA_CASE(2);
+  else if (r <= 4) TIE_DELTA_CASE(4);
+  else if (r <= 8) TIE_DELTA_CASE(8);
+  else if (r <= 16) TIE_DELTA_CASE(16);
+  else TIE_DELTA_CASE(32);
+#undef TIE_DELTA_CASE
+  TIE_RETURN_LAUNCH("delta_rule");
+}
+
+TIE_API int tie_delta_rule(int dtype, const float* qn, const float* kn, const float* vn, const float* beta,
+                           const float* a_raw, long long a_stride, const float* dt_bias, const float* a_log, float* state,
+                           long long state_stride, long long conv_state_off, const void* proj, long long proj_stride,
+                           int q_off, int k_off, int v_off, const int* query_start, const int* state_slots, int seqs,
+                           int heads, int kv_heads, int dim, int vdim, int taps, float* out, cudaStream_t s) {
+  const DeltaShape sh{heads, kv_heads, dim, vdim, taps};
+  if (const int st_ = check_delta(sh)) return st_;
+  if (seqs <= 0) return kOk;
+  TIE_REQUIRE(seqs <= 65535 * 32 && heads <= 65535, "delta_rule: %d sequences x %d heads exceed the grid", seqs, heads);
+  if (dtype == TIE_F32)
+    return launch_delta_rule<float>(qn, kn, vn, beta, a_raw, a_stride, dt_bias, a_log, state, state_stride, conv_state_off, proj,
+                                    proj_stride, q_off, k_off, v_off, query_start, state_slots, seqs, sh, out, s);
+  if (dtype == TIE_BF16)
+    return launch_delta_rule<__nv_bfloat16>(qn, kn, vn, beta, a_raw, a_stride, dt_bias, a_log, state, state_stride, conv_state_off,
+                                            proj, proj_stride, q_off, k_off, v_off, query_start, state_slots, seqs, sh, out, s);
+  set_error("unknown dtype code %d", dtype);
+  return kBadArgument;
+}
+
+TIE_API int tie_delta_out(int dtype, const float* o, const float* gate, long long gate_stride, const float* w, float eps,
+                          void* out, int tokens, int heads, int vdim, cudaStream_t s) {
+  TIE_REQUIRE(tokens >= 0 && heads > 0 && vdim > 0, "delta_out: bad sizes tokens=%d heads=%d vdim=%d", tokens, heads, vdim);
+  const long long items = static_cast<long long>(tokens) * heads;
+  if (items == 0) return kOk;
+  if (dtype == TIE_F32) {
+    TIE_LAUNCH((delta_out_kernel<float>), ceil_div(items, 4), 128, 0, s, o, gate, gate_stride, w, eps, static_cast<float*>(out), heads,
+               vdim, items);
+  } else if (dtype == TIE_BF16) {
+    TIE_LAUNCH((delta_out_kernel<__nv_bfloat16>), ceil_div(items, 4), 128, 0, s, o, gate, gate_stride, w, eps,
+               static_cast<__nv_bfloat16*>(out), heads, vdim, items);
+  } else {
+    set_error("unknown dtype code %d", dtype);
+    return kBadArgument;
+  }
+  TIE_RETURN_LAUNCH("delta_out");
+}

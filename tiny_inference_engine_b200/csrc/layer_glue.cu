@@ -1,0 +1,170 @@
+// Small kernels between the matrix products of layers that norm a sublayer's output before adding it:
+//
+//   add_normed_rmsnorm  x += mult * ((y * inv(y)) * wb),  y = delta (+ bias);  out = (x * inv(x)) * w
+//                       the residual add of a sublayer whose output passes a norm of its own first, fused with
+//                       the norm ahead of the next sublayer. All of it in float: y, both sums, the residual.
+//   glu_clamped         out = g' * sigmoid(slope * g') * (u' + up_shift),  g' = min(g, limit), u' = clamp(u, +-limit)
+//   sigmoid_gate_mul    y *= sigmoid(gate)  (a gate on the heads' outputs)
+//   scale_rows          x *= c  (float rows: the logits of a model that scales them)
+#include <math.h>
+
+#include "common.cuh"
+
+namespace tie {
+
+// One block per output row. The row is kept in shared memory between the passes (dim floats).
+template <typename T>
+__global__ void __launch_bounds__(256) add_normed_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
+                                                                 const float* __restrict__ part, long long part_stride,
+                                                                 int splits, const float* __restrict__ bias,
+                                                                 const float* __restrict__ wb, float eps_b, float mult,
+                                                                 const int* __restrict__ rows, const float* __restrict__ w,
+                                                                 float eps, T* __restrict__ out, int dim) {
+  pdl_sync();
+  extern __shared__ float row[];
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const size_t src = static_cast<size_t>(rows ? rows[t] : t) * dim;
+  float* xr = x + src;
+  const T* dr = delta ? delta + src : nullptr;
+  const float* pr = part ? part + src : nullptr;
+  float ss = 0.0f;
+  for (int k = threadIdx.x; k < dim; k += blockDim.x) {
+    float y;
+    if (dr) {
+      y = ld(dr + k);
+    } else {
+      y = pr[k];
+      for (int z = 1; z < splits; ++z) y += pr[static_cast<long long>(z) * part_stride + k];
+    }
+    if (bias) y += bias[k];
+    row[k] = y;
+    ss += y * y;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv_y = 1.0f / sqrtf(ss / static_cast<float>(dim) + eps_b);
+  float sx = 0.0f;
+  for (int k = threadIdx.x; k < dim; k += blockDim.x) {
+    const float v = xr[k] + mult * ((row[k] * inv_y) * wb[k]);
+    if (rows == nullptr) xr[k] = v;
+    row[k] = v;
+    sx += v * v;
+  }
+  sx = block_sum(sx, scratch);
+  const float inv_x = 1.0f / sqrtf(sx / static_cast<float>(dim) + eps);
+  T* o = out + static_cast<size_t>(t) * dim;
+  for (int k = threadIdx.x; k < dim; k += blockDim.x) st(o + k, (row[k] * inv_x) * w[k]);
+}
+
+template <typename T>
+__global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, long long total, float limit,
+                                   float slope, float up_shift) {
+  pdl_sync();
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / inter;
+  const int c = static_cast<int>(i % inter);
+  const float g = fminf(ld(gu + t * 2 * inter + c), limit);
+  const float u = fminf(fmaxf(ld(gu + t * 2 * inter + inter + c), -limit), limit);
+  st(out + i, (g / (1.0f + expf(-slope * g))) * (u + up_shift));
+}
+
+template <typename T>
+__global__ void sigmoid_gate_mul_kernel(T* __restrict__ y, long long y_stride, const T* __restrict__ gate,
+                                        long long gate_stride, int width, long long total) {
+  pdl_sync();
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / width;
+  const int c = static_cast<int>(i % width);
+  const float g = ld(gate + t * gate_stride + c);
+  T* p = y + t * y_stride + c;
+  st(p, ld(p) / (1.0f + expf(-g)));
+}
+
+__global__ void scale_rows_kernel(float* __restrict__ x, long long stride, int width, long long total, float c) {
+  pdl_sync();
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  x[(i / width) * stride + i % width] *= c;
+}
+
+template <typename T>
+int launch_add_normed_rmsnorm(float* x, const void* delta, const float* part, long long part_stride, int splits,
+                              const float* bias, const float* wb, float eps_b, float mult, const int* rows,
+                              const float* w, float eps, void* out, int n, int dim, cudaStream_t s) {
+  if (n == 0) return kOk;
+  const size_t smem = static_cast<size_t>(dim) * sizeof(float);
+  auto kernel = add_normed_rmsnorm_kernel<T>;
+  if (smem > 48 * 1024) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+      set_error("add_normed_rmsnorm: rows of %d floats do not fit shared memory", dim);
+      return kBadArgument;
+    }
+  }
+  TIE_LAUNCH(kernel, n, dim >= 512 ? 256 : 128, smem, s, x, static_cast<const T*>(delta), part, part_stride, splits, bias, wb,
+             eps_b, mult, rows, w, eps, static_cast<T*>(out), dim);
+  TIE_RETURN_LAUNCH("add_normed_rmsnorm");
+}
+
+}  // namespace tie
+
+using namespace tie;
+
+TIE_API int tie_add_normed_rmsnorm(int dtype, float* x, const void* delta, const float* part, long long part_stride,
+                                   int splits, const float* bias, const float* wb, float eps_b, float mult,
+                                   const int* rows, const float* w, float eps, void* out, int n, int dim, cudaStream_t s) {
+  TIE_REQUIRE(n >= 0 && dim > 0 && dim <= 56 * 1024 && (delta != nullptr || (part != nullptr && splits > 0)),
+              "add_normed_rmsnorm: bad sizes n=%d dim=%d, or nothing to add", n, dim);
+  if (dtype == TIE_F32)
+    return launch_add_normed_rmsnorm<float>(x, delta, part, part_stride, splits, bias, wb, eps_b, mult, rows, w, eps, out, n, dim, s);
+  if (dtype == TIE_BF16)
+    return launch_add_normed_rmsnorm<__nv_bfloat16>(x, delta, part, part_stride, splits, bias, wb, eps_b, mult, rows, w, eps, out, n,
+                                                    dim, s);
+  set_error("unknown dtype code %d", dtype);
+  return kBadArgument;
+}
+
+TIE_API int tie_glu_clamped(int dtype, const void* gu, void* out, int tokens, int inter, float limit, float slope,
+                            float up_shift, cudaStream_t s) {
+  TIE_REQUIRE(tokens >= 0 && inter > 0, "glu_clamped: bad sizes tokens=%d inter=%d", tokens, inter);
+  const long long total = static_cast<long long>(tokens) * inter;
+  if (total == 0) return kOk;
+  if (dtype == TIE_F32) {
+    TIE_LAUNCH((glu_clamped_kernel<float>), ceil_div(total, 256), 256, 0, s, static_cast<const float*>(gu), static_cast<float*>(out),
+               inter, total, limit, slope, up_shift);
+  } else if (dtype == TIE_BF16) {
+    TIE_LAUNCH((glu_clamped_kernel<__nv_bfloat16>), ceil_div(total, 256), 256, 0, s, static_cast<const __nv_bfloat16*>(gu),
+               static_cast<__nv_bfloat16*>(out), inter, total, limit, slope, up_shift);
+  } else {
+    set_error("unknown dtype code %d", dtype);
+    return kBadArgument;
+  }
+  TIE_RETURN_LAUNCH("glu_clamped");
+}
+
+TIE_API int tie_sigmoid_gate_mul(int dtype, void* y, long long y_stride, const void* gate, long long gate_stride, int tokens,
+                                 int width, cudaStream_t s) {
+  TIE_REQUIRE(tokens >= 0 && width > 0, "sigmoid_gate_mul: bad sizes tokens=%d width=%d", tokens, width);
+  const long long total = static_cast<long long>(tokens) * width;
+  if (total == 0) return kOk;
+  if (dtype == TIE_F32) {
+    TIE_LAUNCH((sigmoid_gate_mul_kernel<float>), ceil_div(total, 256), 256, 0, s, static_cast<float*>(y), y_stride,
+               static_cast<const float*>(gate), gate_stride, width, total);
+  } else if (dtype == TIE_BF16) {
+    TIE_LAUNCH((sigmoid_gate_mul_kernel<__nv_bfloat16>), ceil_div(total, 256), 256, 0, s, static_cast<__nv_bfloat16*>(y), y_stride,
+               static_cast<const __nv_bfloat16*>(gate), gate_stride, width, total);
+  } else {
+    set_error("unknown dtype code %d", dtype);
+    return kBadArgument;
+  }
+  TIE_RETURN_LAUNCH("sigmoid_gate_mul");
+}
+
+TIE_API int tie_scale_rows(float* x, long long stride, int rows, int width, float c, cudaStream_t s) {
+  TIE_REQUIRE(rows >= 0 && width > 0, "scale_rows: bad sizes rows=%d width=%d", rows, width);
+  const long long total = static_cast<long long>(rows) * width;
+  if (total == 0) return kOk;
+  TIE_LAUNCH(scale_rows_kernel, ceil_div(total, 256), 256, 0, s, x, stride, width, total, c);
+  TIE_RETURN_LAUNCH("scale_rows");
+}

@@ -499,3 +499,218 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """[I, K], [I, K] -> [2I, K]: 16 gate rows, their 16 up rows, the next 16 gate rows, ... (I % 16 == 0)."""
     I, K = gate.shape
     return torch.stack([gate.view(I // 16, 16, K), up.view(I // 16, 16, K)], dim=1).reshape(2 * I, K).contiguous()
+
+
+# -- layers that norm a sublayer's output before adding it, gated units, scaled logits (csrc/layer_glue.cu)
+
+class NormedDelta:
+    """A sublayer's output that is still to pass a norm of its own and a factor before it joins the residual
+    stream: x += mult * ((y * inv_rms(y)) * weight), y = delta (+ bias). `delta` is a tensor [T, D] in the
+    compute dtype or a SplitSum; `weight` float32 [D]; `bias` float32 [D] or None."""
+
+    def __init__(self, delta, weight: torch.Tensor, eps: float, mult: float, bias=None):
+        self.delta, self.weight, self.eps, self.mult, self.bias = delta, weight, float(eps), float(mult), bias
+
+
+def add_normed_rmsnorm(x: torch.Tensor, pending: NormedDelta, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                       rows=None) -> None:
+    """x += mult * norm_b(delta + bias) (float32, in place), out = rmsnorm(x) * weight in out's dtype. With `rows`
+    (int32 [R]) out[i] comes from row rows[i] and x is left as it is."""
+    part, delta = None, pending.delta
+    if isinstance(delta, SplitSum):
+        part, delta = delta, None
+        _need(part.M == x.shape[0] and part.N == x.shape[-1], "add_normed_rmsnorm: partial sums do not match x")
+    _dev(x, delta, weight, out, rows, pending.weight, pending.bias)
+    D, n = x.shape[-1], out.shape[0]
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "add_normed_rmsnorm: x must be float32 contiguous")
+    for w in (weight, pending.weight, pending.bias):
+        _need(w is None or (w.dtype == torch.float32 and w.numel() == D), "add_normed_rmsnorm: weights and bias must be float32 [D]")
+    _need(out.shape[-1] == D and out.is_contiguous(), "add_normed_rmsnorm: out must be [n, D] contiguous")
+    if delta is not None:
+        _need(delta.dtype == out.dtype and delta.shape == x.shape and delta.is_contiguous(),
+              "add_normed_rmsnorm: delta must match x's shape and out's dtype")
+    if rows is None:
+        _need(n == x.shape[0], "add_normed_rmsnorm: out must have x's rows")
+    else:
+        _need(rows.dtype == torch.int32 and rows.numel() == n, "add_normed_rmsnorm: rows must be int32 [n]")
+    call("tie_add_normed_rmsnorm", dtype_code(out), x.data_ptr(), _ptr(delta), part.partial.data_ptr() if part else 0,
+         part.stride if part else 0, part.splits if part else 0, _ptr(pending.bias), pending.weight.data_ptr(), pending.eps,
+         pending.mult, _ptr(rows), weight.data_ptr(), float(eps), out.data_ptr(), n, D, _stream())
+
+
+def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: float, up_shift: float) -> None:
+    """out[t, i] = g sigmoid(slope g) (u + up_shift), g = min(gate_up[t, i], limit), u = clamp(gate_up[t, I + i], -limit, limit)."""
+    _dev(gate_up, out)
+    T, I = out.shape
+    _need(gate_up.shape == (T, 2 * I) and gate_up.is_contiguous() and out.is_contiguous() and gate_up.dtype == out.dtype,
+          "glu_clamped: gate_up must be [T, 2I] and out [T, I], same dtype, contiguous")
+    call("tie_glu_clamped", dtype_code(out), gate_up.data_ptr(), out.data_ptr(), T, I, float(limit), float(slope),
+         float(up_shift), _stream())
+
+
+def sigmoid_gate_mul(y: torch.Tensor, gate: torch.Tensor) -> None:
+    """y *= sigmoid(gate), in place; both [T, W] with contiguous last axes (rows may be strided)."""
+    _dev(y, gate)
+    _need(y.dim() == 2 and y.shape == gate.shape and y.dtype == gate.dtype and y.stride(1) == 1 and gate.stride(1) == 1,
+          "sigmoid_gate_mul: y and gate must be [T, W] alike")
+    call("tie_sigmoid_gate_mul", dtype_code(y), y.data_ptr(), y.stride(0), gate.data_ptr(), gate.stride(0), y.shape[0],
+         y.shape[1], _stream())
+
+
+def scale_rows(x: torch.Tensor, c: float) -> None:
+    """x *= c for float32 rows, in place."""
+    _dev(x)
+    _need(x.dim() == 2 and x.dtype == torch.float32 and x.stride(1) == 1, "scale_rows: x must be float32 rows")
+    call("tie_scale_rows", x.data_ptr(), x.stride(0), x.shape[0], x.shape[1], float(c), _stream())
+
+
+# -- attention with an RMS norm over the whole projection, biases, blended values, keys and values of two sizes
+
+def _check_kv_planes(k_cache, v_cache, kv_heads, head_dim, v_dim):
+    _need(k_cache.dim() == 4 and v_cache.dim() == 4 and k_cache.is_contiguous() and v_cache.is_contiguous() and
+          k_cache.shape[:3] == v_cache.shape[:3] and k_cache.dtype == v_cache.dtype,
+          "cache planes must be [pages, kv_heads, page_size, size] contiguous, alike but for the size")
+    _need(k_cache.shape[1] == kv_heads and k_cache.shape[3] == head_dim and v_cache.shape[3] == v_dim,
+          "cache planes do not match the heads")
+    _need(max(k_cache.numel() // head_dim, v_cache.numel() // v_dim) < 2 ** 31, "cache plane too large for 32-bit row indices")
+
+
+def qkv_span_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, bq, bk, bv, wq, wk, eps: float, inv_freq,
+                  positions: torch.Tensor, slots, k_cache, v_cache, q_heads: int, kv_heads: int, head_dim: int, v_dim: int,
+                  mix_mode: int = 0, v_first=None, mix_weight=None, write_kv: bool = True) -> None:
+    """proj [T, >= ...] holds the q, k and v projections of every token at columns q_off, k_off, v_off. q gets its
+    bias, the RMS norm over all of its heads at once (weights wq, float32 [q_heads * head_dim]) and the rotation of
+    the first 2 * len(inv_freq) dimensions of each head, and is written back in place; k likewise into the key
+    plane; v gets its bias, is kept as `v_first` (mix_mode 1) or blended with it, (1 - w) v + w v_first (mix_mode 2,
+    `mix_weight` a float32 device scalar), and goes into the value plane."""
+    _dev(proj, bq, bk, bv, wq, wk, inv_freq, positions, slots, k_cache, v_cache, v_first, mix_weight)
+    T = proj.shape[0]
+    nq, nk, nv = q_heads * head_dim, kv_heads * head_dim, kv_heads * v_dim
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and q_off + nq <= proj.shape[1], "qkv_span_prep: q outside the projection")
+    _need(positions.dtype == torch.int32 and positions.numel() == T, "qkv_span_prep: positions must be int32 [T]")
+    for t, n in ((bq, nq), (bk, nk), (bv, nv), (wq, nq), (wk, nk)):
+        _need(t is None or (t.dtype == torch.float32 and t.numel() == n), "qkv_span_prep: biases and norm weights must be float32 of the projection's size")
+    _need(inv_freq is None or inv_freq.dtype == torch.float32, "qkv_span_prep: inv_freq must be float32")
+    page = 1
+    if write_kv:
+        _need(max(k_off + nk, v_off + nv) <= proj.shape[1], "qkv_span_prep: k or v outside the projection")
+        _check_kv_planes(k_cache, v_cache, kv_heads, head_dim, v_dim)
+        _need(k_cache.dtype == proj.dtype, "qkv_span_prep: dtype differs from the cache's")
+        _need(slots.dtype == torch.int32 and slots.numel() == T, "qkv_span_prep: slots must be int32 [T]")
+        page = k_cache.shape[2]
+        if mix_mode:
+            _need(v_first is not None and v_first.dtype == torch.float32 and v_first.is_contiguous() and
+                  v_first.shape == (T, nv), "qkv_span_prep: v_first must be float32 [T, kv_heads * v_dim]")
+            _need(mix_mode == 1 or (mix_weight is not None and mix_weight.dtype == torch.float32 and mix_weight.numel() == 1),
+                  "qkv_span_prep: the blend's weight must be a float32 scalar on the device")
+    call("tie_qkv_span_prep", dtype_code(proj), proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, _ptr(bq), _ptr(bk), _ptr(bv),
+         _ptr(wq), _ptr(wk), float(eps), _ptr(inv_freq), 2 * inv_freq.numel() if inv_freq is not None else 0,
+         positions.data_ptr(), _ptr(slots) if write_kv else 0, _ptr(k_cache) if write_kv else 0,
+         _ptr(v_cache) if write_kv else 0, T, q_heads, kv_heads, head_dim, v_dim, page, int(mix_mode) if write_kv else 0,
+         _ptr(v_first), _ptr(mix_weight), _stream())
+
+
+def _attn_common_dv(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim, v_dim):
+    _check_kv_planes(k_cache, v_cache, kv_heads, head_dim, v_dim)
+    _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= q_heads * head_dim, "attention: q too narrow")
+    _need(out.shape == (q.shape[0], q_heads * v_dim) and out.is_contiguous(), "attention: out must be [T, Hq*Dv]")
+    _need(q.dtype == k_cache.dtype and out.dtype == q.dtype, "attention: q, cache and out must have one dtype")
+    vec = 4 if q.dtype == torch.float32 else 8
+    _need(head_dim % vec == 0 and q.stride(0) % vec == 0, f"attention: head size and row stride must be multiples of {vec}")
+    S = context_lens.numel()
+    _need(query_start.dtype == torch.int32 and query_start.numel() == S + 1, "attention: query_start must be int32 [S+1]")
+    _need(context_lens.dtype == torch.int32, "attention: context_lens must be int32 [S]")
+    _need(block_tables.dtype == torch.int32 and block_tables.dim() == 2 and block_tables.shape[0] == S and
+          block_tables.is_contiguous(), "attention: block_tables must be int32 [S, max_blocks]")
+    return S
+
+
+def attention_rows_dv(q, k_cache, v_cache, out, seq_of_row, query_start, context_lens, block_tables, q_heads, kv_heads,
+                      head_dim, v_dim, scale: float, window: int = 0) -> None:
+    """`attention_rows` for keys of head_dim and values of v_dim (out [T, q_heads * v_dim])."""
+    _dev(q, k_cache, v_cache, out, seq_of_row, query_start, context_lens, block_tables)
+    S = _attn_common_dv(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim, v_dim)
+    _need(seq_of_row.dtype == torch.int32 and seq_of_row.numel() == q.shape[0], "attention: seq_of_row must be int32 [T]")
+    call("tie_attention_rows_dv", dtype_code(q), q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+         out.data_ptr(), seq_of_row.data_ptr(), query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(),
+         block_tables.shape[1], q.shape[0], S, q_heads, kv_heads, head_dim, v_dim, k_cache.shape[2], int(window), float(scale),
+         _stream())
+
+
+def attention_split_dv(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim, v_dim,
+                       scale: float, seq_list, n_list: int, split_keys: int, max_splits: int, scratch, window: int = 0) -> None:
+    """`attention_split` for keys of head_dim and values of v_dim; scratch holds
+    attention_split_scratch_floats(n_list, q_heads, v_dim, max_splits) floats."""
+    _dev(q, k_cache, v_cache, out, query_start, context_lens, block_tables, seq_list, scratch)
+    S = _attn_common_dv(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim, v_dim)
+    _need(seq_list.dtype == torch.int32 and seq_list.numel() >= n_list, "attention: seq_list must be int32 [n_list]")
+    _need(scratch.dtype == torch.float32 and
+          scratch.numel() >= attention_split_scratch_floats(n_list, q_heads, v_dim, max_splits), "attention: scratch too small")
+    call("tie_attention_split_dv", dtype_code(q), q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+         out.data_ptr(), query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
+         S, q_heads, kv_heads, head_dim, v_dim, k_cache.shape[2], int(window), float(scale), seq_list.data_ptr(), n_list,
+         split_keys, max_splits, scratch.data_ptr(), _stream())
+
+
+# -- the gated delta rule with a decay per key channel (csrc/delta_rule.cu)
+
+def delta_prep(proj, q_off: int, k_off: int, v_off: int, b_off: int, conv_w, state, conv_state_off: int, seq_of_row,
+               query_start, state_slots, heads: int, kv_heads: int, dim: int, vdim: int, taps: int, unit_eps: float,
+               q_scale: float, qn, kn, vn, beta) -> None:
+    """Short causal convolution + SiLU of the q, k, v columns of `proj`, unit norm of q and k per head (q times
+    q_scale), sigmoid of the beta columns. `state` [slots, floats] holds, from conv_state_off on, each sequence's
+    last taps - 1 convolution inputs. Outputs are float32: qn, kn [T, kv_heads * dim], vn [T, heads * vdim], beta [T, heads]."""
+    _dev(proj, conv_w, state, seq_of_row, query_start, state_slots, qn, kn, vn, beta)
+    T = proj.shape[0]
+    nqk, nv = kv_heads * dim, heads * vdim
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and max(q_off + nqk, k_off + nqk, v_off + nv, b_off + heads) <= proj.shape[1],
+          "delta_prep: columns outside the projection")
+    _need(conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape == (2 * nqk + nv, taps),
+          "delta_prep: convolution weights must be float32 [channels, taps]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and
+          conv_state_off + (taps - 1) * (2 * nqk + nv) <= state.shape[1], "delta_prep: state rows too short")
+    for t, n in ((qn, nqk), (kn, nqk), (vn, nv), (beta, heads)):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, n), "delta_prep: outputs must be float32 [T, n]")
+    for t in (seq_of_row, query_start, state_slots):
+        _need(t.dtype == torch.int32, "delta_prep: index tensors must be int32")
+    call("tie_delta_prep", dtype_code(proj), proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, b_off, conv_w.data_ptr(),
+         state.data_ptr(), state.stride(0), conv_state_off, seq_of_row.data_ptr(), query_start.data_ptr(),
+         state_slots.data_ptr(), T, heads, kv_heads, dim, vdim, taps, float(unit_eps), float(q_scale), qn.data_ptr(),
+         kn.data_ptr(), vn.data_ptr(), beta.data_ptr(), _stream())
+
+
+def delta_rule(qn, kn, vn, beta, a_raw, dt_bias, a_log, state, conv_state_off: int, proj, q_off: int, k_off: int, v_off: int,
+               query_start, state_slots, seqs: int, heads: int, kv_heads: int, dim: int, vdim: int, taps: int, out) -> None:
+    """The recurrence over each sequence's tokens of the step: per head S <- decay S; u = beta (v - S^T k);
+    S <- S + k u^T; o = S^T q, with decay = exp(-exp(a_log[h]) softplus(a_raw + dt_bias)) per key channel.
+    S [heads, dim, vdim] sits at the start of the sequence's row of `state` and is updated; so are the convolution's
+    last inputs (from the q, k, v columns of `proj`). `a_raw` float32 [T, >= heads * dim] (rows may be strided);
+    out float32 [T, heads * vdim]."""
+    _dev(qn, kn, vn, beta, a_raw, dt_bias, a_log, state, proj, query_start, state_slots, out)
+    T = proj.shape[0]
+    _need(a_raw.dtype == torch.float32 and a_raw.dim() == 2 and a_raw.stride(1) == 1 and a_raw.shape[0] == T and
+          a_raw.shape[1] >= heads * dim, "delta_rule: a_raw must be float32 [T, >= heads * dim]")
+    _need(dt_bias.dtype == torch.float32 and dt_bias.numel() == heads * dim and a_log.dtype == torch.float32 and
+          a_log.numel() == heads, "delta_rule: dt_bias float32 [heads * dim], a_log float32 [heads]")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (T, heads * vdim), "delta_rule: out must be float32 [T, heads * vdim]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and conv_state_off >= heads * dim * vdim,
+          "delta_rule: state rows too short")
+    _need(query_start.numel() >= seqs + 1 and state_slots.numel() >= seqs, "delta_rule: index tensors too short")
+    call("tie_delta_rule", dtype_code(proj), qn.data_ptr(), kn.data_ptr(), vn.data_ptr(), beta.data_ptr(), a_raw.data_ptr(),
+         a_raw.stride(0), dt_bias.data_ptr(), a_log.data_ptr(), state.data_ptr(), state.stride(0), conv_state_off,
+         proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, query_start.data_ptr(), state_slots.data_ptr(), seqs, heads,
+         kv_heads, dim, vdim, taps, out.data_ptr(), _stream())
+
+
+def delta_out(o, gate, weight, eps: float, out, heads: int, vdim: int) -> None:
+    """out[t, h] = (o[t, h] / rms(o[t, h])) * weight * sigmoid(gate[t, h]) per head of vdim; o, gate float32, out in
+    the compute dtype."""
+    _dev(o, gate, weight, out)
+    T = o.shape[0]
+    _need(o.dtype == torch.float32 and o.is_contiguous() and o.shape == (T, heads * vdim), "delta_out: o must be float32 [T, heads * vdim]")
+    _need(gate.dtype == torch.float32 and gate.dim() == 2 and gate.stride(1) == 1 and gate.shape == o.shape,
+          "delta_out: gate must be float32 [T, heads * vdim]")
+    _need(weight.dtype == torch.float32 and weight.numel() == vdim, "delta_out: weight must be float32 [vdim]")
+    _need(out.is_contiguous() and out.shape == o.shape, "delta_out: out must be [T, heads * vdim] contiguous")
+    call("tie_delta_out", dtype_code(out), o.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(), float(eps),
+         out.data_ptr(), T, heads, vdim, _stream())

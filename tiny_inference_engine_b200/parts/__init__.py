@@ -2,7 +2,7 @@
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Block, CacheNeed,
                    Embedding, FeedForward, Mixer, Norm, OutputHead, Part, PositionEncoding, StateNeed, build_part,
                    register_part, to_compute)
-from . import norm, position, attention, feed_forward, block, embedding  # noqa: F401  (register the built-in kinds)
+from . import norm, position, attention, gated_attention, delta, feed_forward, block, embedding  # noqa: F401  (register the built-in kinds)
 from .attention import GQAttention
 from .block import PreNormBlock
 from .embedding import LMHead, TokenEmbedding

@@ -21,11 +21,13 @@ from ..weights.loader import TensorNeed
 @dataclass(frozen=True)
 class CacheNeed:
     """What a mixer wants of the paged cache: keys and values of `kv_heads` x `head_dim` per
-    token; kind "full" keeps every token, "window" only the last `window`."""
+    token; kind "full" keeps every token, "window" only the last `window`. `value_dim` is the
+    size of a value head where it differs from a key head's (0: the same)."""
     kind: str
     kv_heads: int
     head_dim: int
     window: int = 0
+    value_dim: int = 0
 
 
 @dataclass(frozen=True)

@@ -35,6 +35,7 @@ class LMHead(OutputHead):
         self.name = spec["name"]
         self.tied = bool(spec["tied"])
         self.vocab, self.hidden = int(spec["vocab_size"]), int(spec["hidden_size"])
+        self.logit_scale = float(spec.params.get("logit_scale", 1.0))      # a constant factor on the float32 logits
         self.dtype = dtype
         self.embedding = embedding
         self.weight = None
@@ -54,6 +55,8 @@ class LMHead(OutputHead):
 
     def forward(self, last, logits):
         self.product(last, logits)
+        if self.logit_scale != 1.0:
+            ops.scale_rows(logits, self.logit_scale)
 
 
 register_part("embedding", "token_embedding", TokenEmbedding, replace=True)

@@ -54,4 +54,43 @@ class SwiGLU(FeedForward):
         return self.down(act, out, lambda n: ctx.ws.flat("ffn.out.partial", n, torch.float32, self._partial_capacity))
 
 
+class ClampedGLU(FeedForward):
+    """A gated unit with clamped branches: g = min(gate(h), limit), u = clamp(up(h), -limit, limit),
+    y = g * sigmoid(slope * g) * (u + up_shift), then down(y). params: `hidden_size`, `intermediate_size`, `limit`,
+    `slope`, `up_shift`, and the three tensors' names (`gate`, `up`, `down`) after `prefix`."""
+    launches_only = False
+
+    def __init__(self, spec, dtype, prefix: str = ""):
+        p = spec.params
+        self.prefix = prefix + p.get("prefix", "")
+        self.hidden, self.inter = int(p["hidden_size"]), int(p["intermediate_size"])
+        self.limit, self.slope, self.up_shift = float(p["limit"]), float(p.get("slope", 1.0)), float(p.get("up_shift", 0.0))
+        self.names = tuple(self.prefix + p.get(k, k) for k in ("gate", "up", "down"))
+        self.dtype = dtype
+        self._partial_capacity = None
+
+    def needs(self):
+        return {self.names[0]: TensorNeed((self.inter, self.hidden)), self.names[1]: TensorNeed((self.inter, self.hidden)),
+                self.names[2]: TensorNeed((self.hidden, self.inter))}
+
+    def bind(self, get):
+        gate, up = (to_compute(get(n), self.dtype) for n in self.names[:2])
+        self.gate_up = ops.bound_gemm(torch.cat([gate, up], dim=0).contiguous(), split_many=False)
+        del gate, up
+        self.down = ops.bound_gemm(to_compute(get(self.names[2]), self.dtype).contiguous())
+        self.w_gate_up, self.w_down = self.gate_up.w, self.down.w
+
+    def forward(self, h, ctx):
+        T = h.shape[0]
+        gu = ctx.ws.rows("ffn.gate_up", T, 2 * self.inter, self.dtype)
+        self.gate_up(h, gu)
+        act = ctx.ws.rows("ffn.act", T, self.inter, self.dtype)
+        ops.glu_clamped(gu, act, self.limit, self.slope, self.up_shift)
+        out = ctx.ws.rows("ffn.out", T, self.hidden, self.dtype)
+        if self._partial_capacity is None:
+            self._partial_capacity = ops.partial_capacity(ctx.ws.max_rows, self.down.N, self.down.K)
+        return self.down(act, out, lambda n: ctx.ws.flat("ffn.out.partial", n, torch.float32, self._partial_capacity))
+
+
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)
+register_part("feed_forward", "clamped_glu", ClampedGLU, replace=True)

@@ -29,10 +29,24 @@ class RMSNorm(Norm):
         self.weight = get(self.name).to(torch.float32).contiguous()
 
     def add_norm(self, x, delta, out, rows=None):
-        ops.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)
+        if isinstance(delta, ops.NormedDelta):      # a sublayer's output that passes a norm of its own on its way in
+            ops.add_normed_rmsnorm(x, delta, self.weight, self.eps, out, rows)
+        else:
+            ops.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)
 
     def rows(self, x, out):
         ops.rmsnorm_rows(x, self.weight, self.eps, out)
 
 
 register_part("norm", "rmsnorm", RMSNorm, replace=True)
+
+
+class RMSNormOnePlus(RMSNorm):
+    """RMSNorm whose weight is stored as its distance from one: (x / sqrt(mean(x^2) + eps)) * (1 + w). The sum
+    1 + w is formed once, in float32, when the weight is bound; after that it is the formula of `RMSNorm`."""
+
+    def bind(self, get):
+        self.weight = (get(self.name).to(torch.float32) + 1.0).contiguous()
+
+
+register_part("norm", "rmsnorm_one_plus", RMSNormOnePlus, replace=True)
