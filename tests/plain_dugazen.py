@@ -43,14 +43,33 @@ def rms(x, eps):
     return x / np.sqrt((x * x).mean(axis=-1, keepdims=True) + eps)
 
 
+_act = None       # with `bfloat16_activations()`: rounds what a 16-bit pipeline would keep in 16 bits
+
+
+class bfloat16_activations:
+    """Within this context the outputs of `linear` and of the layers' norms are rounded to bfloat16 (the weights
+    of the tests are bfloat16 values already): the difference to the exact result is the noise that a pipeline
+    with 16-bit activations cannot avoid, which is what a tolerance for such a pipeline is measured against."""
+
+    def __enter__(self):
+        global _act
+        _act = lambda y: round_bf16(y).astype(np.float64)
+
+    def __exit__(self, *exc):
+        global _act
+        _act = None
+
+
 def norm_one_plus(x, w, eps):
     """The layers' norm: the weight is stored as its distance from one."""
-    return rms(x, eps) * (1.0 + np.asarray(w, dtype=np.float64))
+    y = rms(x, eps) * (1.0 + np.asarray(w, dtype=np.float64))
+    return y if _act is None else _act(y)
 
 
 def linear(x, w, b=None):
     y = np.asarray(x, dtype=np.float64) @ np.asarray(w, dtype=np.float64).T
-    return y if b is None else y + np.asarray(b, dtype=np.float64)
+    y = y if b is None else y + np.asarray(b, dtype=np.float64)
+    return y if _act is None else _act(y)
 
 
 # --------------------------------------------------------------------------- attention layer
@@ -106,7 +125,7 @@ def attention_mixer(h, w, p, mx, eps, positions, v_first):
         if v_first is None:
             v_first = v
         else:
-            lam = float(np.asarray(w[p + "vmix"], dtype=np.float64))
+            lam = float(np.asarray(w[p + "vmix"], dtype=np.float64).reshape(()))
             v = (1.0 - lam) * v + lam * v_first
     o = windowed_attention(q, k, v, H, G, dim, vdim, mx["scale"], mx["mask"]["size"])
     o = o * sigmoid(linear(h, w[p + "g"]))
@@ -201,6 +220,14 @@ def forward(w, cfg, tokens, layers_out=None):
     return linear(norm_one_plus(x, w["final.norm"], eps), w["head"]) * cfg["logit_scale"]
 
 
+def generate(w, cfg, prompt, n):
+    """Greedy: n tokens after the prompt, each the argmax of the logits at the last position."""
+    tokens = list(prompt)
+    for _ in range(n):
+        tokens.append(int(np.argmax(forward(w, cfg, tokens)[-1])))
+    return tokens[len(prompt):]
+
+
 # --------------------------------------------------------------------------- configurations and weights for tests
 
 def attention_layer(heads=4, kv_heads=2, dim=32, vdim=16, window=24, rot_dims=16, base=10000.0, scale=None,
@@ -223,8 +250,10 @@ def make_config(layers, vocab=160, width=64, eps=1e-6, residual_mult=0.5, logit_
             "residual_mult": residual_mult, "vocab": vocab, "width": width}
 
 
-def tensor_shapes(cfg, low_rank=8):
-    """name -> shape. The two-step projections of a channel_delta layer (a1/a2, g1/g2) meet at `low_rank`."""
+def tensor_shapes(cfg, low_rank=8, gate_rank=None):
+    """name -> shape. The two-step projections of a channel_delta layer meet at `low_rank` (a1/a2) and
+    `gate_rank` (g1/g2; None: the same)."""
+    gate_rank = low_rank if gate_rank is None else gate_rank
     D = cfg["width"]
     s = {"embed": (cfg["vocab"], D), "final.norm": (D,), "head": (cfg["vocab"], D)}
     for i, layer in enumerate(cfg["layers"]):
@@ -243,7 +272,7 @@ def tensor_shapes(cfg, low_rank=8):
                       p + "mix.k.conv": (G * dim, mx["conv"]), p + "mix.v": (H * vdim, D),
                       p + "mix.v.conv": (H * vdim, mx["conv"]), p + "mix.b": (H, D), p + "mix.A_log": (H,),
                       p + "mix.norm": (vdim,), p + "mix.a1": (low_rank, D), p + "mix.a2": (H * dim, low_rank),
-                      p + "mix.dt_bias": (H * dim,), p + "mix.g1": (low_rank, D), p + "mix.g2": (H * vdim, low_rank),
+                      p + "mix.dt_bias": (H * dim,), p + "mix.g1": (gate_rank, D), p + "mix.g2": (H * vdim, gate_rank),
                       p + "mix.o": (D, H * vdim)})
         if layer.get("mlp") is not None:
             ff = layer["mlp"]["ff"]
@@ -256,16 +285,16 @@ def round_bf16(x):
     a = np.ascontiguousarray(x, dtype=np.float32)
     bits = a.view(np.uint32).astype(np.uint64)
     rounded = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) << 16
-    return rounded.astype(np.uint32).view(np.float32).reshape(a.shape)
+    return rounded.astype(np.uint32).view(np.float32).reshape(np.shape(x))      # (a scalar stays a scalar)
 
 
-def random_weights(cfg, seed, low_rank=8, sharp=4.0):
+def random_weights(cfg, seed, low_rank=8, sharp=4.0, gate_rank=None):
     """float32 weights that bfloat16 holds exactly (so that both dtypes load the same model). Matrices are
     N(0, 1/in); norm weights and biases are small; q and k projections of attention layers are `sharp`
     times larger so that attention is not flat and a key that is lost or misplaced moves the logits."""
     rng = np.random.default_rng(seed)
     w = {}
-    for name, shape in tensor_shapes(cfg, low_rank).items():
+    for name, shape in tensor_shapes(cfg, low_rank, gate_rank).items():
         leaf = name.split(".")[-1]
         if name in ("embed",):
             t = rng.standard_normal(shape)
@@ -297,14 +326,15 @@ def write_safetensors(path, tensors, bf16=True):
     """One file: 8-byte little-endian header length, JSON header, data. bf16 stores the upper 16 bits."""
     header, blobs, off = {}, [], 0
     for name, t in tensors.items():
-        a = np.ascontiguousarray(t, dtype=np.float32)
+        shape = list(np.shape(t))                      # (a scalar keeps the shape [])
+        a = np.ascontiguousarray(t, dtype=np.float32).reshape(-1)
         if bf16:
             data = (a.view(np.uint32) >> 16).astype("<u2").tobytes()
             dt = "BF16"
         else:
             data = a.astype("<f4").tobytes()
             dt = "F32"
-        header[name] = {"dtype": dt, "shape": list(a.shape), "data_offsets": [off, off + len(data)]}
+        header[name] = {"dtype": dt, "shape": shape, "data_offsets": [off, off + len(data)]}
         blobs.append(data)
         off += len(data)
     hj = json.dumps(header).encode()

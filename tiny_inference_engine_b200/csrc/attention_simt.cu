@@ -62,11 +62,15 @@ __device__ __forceinline__ void attend_range(const float* __restrict__ qs, const
       row = (page * kv_heads + kvh) * page_size + j % page_size;
       const T* kr = kc + static_cast<long long>(row) * head_dim;
       float dot = 0.0f;
-      for (int d = 0; d < head_dim; d += V) {
-        Vec16<T> kv;
-        kv.load(kr + d);
+      if (head_dim % V == 0) {      // rows of whole 16-byte pieces
+        for (int d = 0; d < head_dim; d += V) {
+          Vec16<T> kv;
+          kv.load(kr + d);
 #pragma unroll
-        for (int e = 0; e < V; ++e) dot = fmaf(qs[d + e], kv.v[e], dot);
+          for (int e = 0; e < V; ++e) dot = fmaf(qs[d + e], kv.v[e], dot);
+        }
+      } else {
+        for (int d = 0; d < head_dim; ++d) dot = fmaf(qs[d], ld(kr + d), dot);
       }
       s = scale * dot;
     }
@@ -84,7 +88,8 @@ __device__ __forceinline__ void attend_range(const float* __restrict__ qs, const
       if (d0 < v_dim) {
         const T* vr = vc + static_cast<long long>(rj) * v_dim + d0;
 #pragma unroll
-        for (int e = 0; e < DPL; ++e) acc[e] = fmaf(pj, ld(vr + e), acc[e]);
+        for (int e = 0; e < DPL; ++e)
+          if (d0 + e < v_dim) acc[e] = fmaf(pj, ld(vr + e), acc[e]);
       }
     }
   }
@@ -119,7 +124,8 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnArgs a) {
     T* o = static_cast<T*>(a.out) + (static_cast<long long>(t) * a.q_heads + h) * a.v_dim + d0;
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;  // no keys (a padding row): zeros
 #pragma unroll
-    for (int e = 0; e < DPL; ++e) st(o + e, acc[e] * inv);
+    for (int e = 0; e < DPL; ++e)
+      if (d0 + e < a.v_dim) st(o + e, acc[e] * inv);
   }
 }
 
@@ -160,7 +166,8 @@ __global__ void __launch_bounds__(128) attention_split_kernel(AttnArgs a, const 
   const int d0 = lane * DPL;
   if (d0 < a.v_dim) {
 #pragma unroll
-    for (int e = 0; e < DPL; ++e) dst[d0 + e] = acc[e];
+    for (int e = 0; e < DPL; ++e)
+      if (d0 + e < a.v_dim) dst[d0 + e] = acc[e];
   }
   if (lane == 0) {
     dst[a.v_dim] = m;
@@ -253,13 +260,17 @@ int launch_attention(const AttnArgs& a, const int* row_seq_unused, const int* se
 
 using namespace tie;
 
-static int check_attn(const AttnArgs& a) {
+// `any_size`: the launchers for keys and values of two sizes take heads of any size (rows that are not whole
+// 16-byte pieces are read element by element); the others keep the sizes that the tensor-core kernels share.
+static int check_attn(const AttnArgs& a, bool any_size = false) {
   TIE_REQUIRE(a.q_heads > 0 && a.kv_heads > 0 && a.q_heads % a.kv_heads == 0,
               "attention: %d query heads are not a multiple of %d kv heads", a.q_heads, a.kv_heads);
-  TIE_REQUIRE(a.head_dim > 0 && a.head_dim % 8 == 0 && a.head_dim <= 512,
-              "attention: head_dim %d must be a multiple of 8 and at most 512", a.head_dim);
-  TIE_REQUIRE(a.head_dim <= 256 || a.head_dim % 16 == 0, "attention: head_dim %d above 256 must be a multiple of 16",
-              a.head_dim);
+  TIE_REQUIRE(a.head_dim > 0 && a.head_dim <= 512, "attention: head_dim %d must be 1 to 512", a.head_dim);
+  if (!any_size) {
+    TIE_REQUIRE(a.head_dim % 8 == 0, "attention: head_dim %d must be a multiple of 8 and at most 512", a.head_dim);
+    TIE_REQUIRE(a.head_dim <= 256 || a.head_dim % 16 == 0, "attention: head_dim %d above 256 must be a multiple of 16",
+                a.head_dim);
+  }
   TIE_REQUIRE(a.v_dim > 0 && a.v_dim <= 512, "attention: value heads of %d (1 to 512)", a.v_dim);
   TIE_REQUIRE(a.page_size > 0 && a.max_blocks > 0, "attention: bad page geometry");
   TIE_REQUIRE(a.window >= 0, "attention: negative window");
@@ -335,7 +346,7 @@ TIE_API int tie_attention_rows_dv(int dtype, const void* q, long long q_stride, 
                                   int head_dim, int v_dim, int page_size, int window, float scale, cudaStream_t s) {
   const AttnArgs a{q, k_cache, v_cache, out, seq_of_row, query_start, context_lens, block_tables, q_stride, max_blocks,
                    rows, seqs, q_heads, kv_heads, head_dim, page_size, window, scale, v_dim};
-  if (const int st = check_attn(a)) return st;
+  if (const int st = check_attn(a, true)) return st;
   if (dtype == TIE_F32) return launch_attention<float>(a, nullptr, nullptr, 0, 0, 0, nullptr, 1, s);
   if (dtype == TIE_BF16) return launch_attention<__nv_bfloat16>(a, nullptr, nullptr, 0, 0, 0, nullptr, 1, s);
   set_error("attention: unknown dtype code %d", dtype);
@@ -349,7 +360,7 @@ TIE_API int tie_attention_split_dv(int dtype, const void* q, long long q_stride,
                                    int max_splits, float* scratch, cudaStream_t s) {
   const AttnArgs a{q, k_cache, v_cache, out, nullptr, query_start, context_lens, block_tables, q_stride, max_blocks,
                    0, seqs, q_heads, kv_heads, head_dim, page_size, window, scale, v_dim};
-  if (const int st = check_attn(a)) return st;
+  if (const int st = check_attn(a, true)) return st;
   TIE_REQUIRE(split_keys > 0 && max_splits > 0 && max_splits <= kMergeMaxSplits && scratch != nullptr,
               "attention split: bad split geometry (at most %d splits)", kMergeMaxSplits);
   if (dtype == TIE_F32) return launch_attention<float>(a, nullptr, seq_list, n_list, split_keys, max_splits, scratch, 0, s);

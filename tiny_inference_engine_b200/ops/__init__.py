@@ -615,8 +615,6 @@ def _attn_common_dv(q, k_cache, v_cache, out, query_start, context_lens, block_t
     _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= q_heads * head_dim, "attention: q too narrow")
     _need(out.shape == (q.shape[0], q_heads * v_dim) and out.is_contiguous(), "attention: out must be [T, Hq*Dv]")
     _need(q.dtype == k_cache.dtype and out.dtype == q.dtype, "attention: q, cache and out must have one dtype")
-    vec = 4 if q.dtype == torch.float32 else 8
-    _need(head_dim % vec == 0 and q.stride(0) % vec == 0, f"attention: head size and row stride must be multiples of {vec}")
     S = context_lens.numel()
     _need(query_start.dtype == torch.int32 and query_start.numel() == S + 1, "attention: query_start must be int32 [S+1]")
     _need(context_lens.dtype == torch.int32, "attention: context_lens must be int32 [S]")
