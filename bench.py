@@ -178,6 +178,121 @@ def serving_mix(args) -> dict:
         "data": "synthetic (random weights N(0,0.02), uniform random token ids, all requests at time 0)"}
 
 
+# -- the Dugazen design beside Qwen3 at equal sizes (`--design dugazen`; a line of its own, not the contract line)
+
+def dugazen_config(width, layers, heads, kv_heads, ff, vocab, window=1024, vdim=128):
+    """Attention and delta-rule layers in turn, every layer with a feed-forward, at the sizes of a Qwen3 layer."""
+    att = {"type": "attention", "mixer": {"dim": 128, "heads": heads, "kv_heads": kv_heads, "mask": {"size": window},
+                                           "rot": {"base": 1000000.0, "dims": 64}, "scale": 128 ** -0.5, "v_mix": True, "vdim": vdim},
+           "mlp": {"ff": ff, "kind": "dense", "limit": 7.0}}
+    delta = {"type": "channel_delta", "mixer": {"conv": 4, "dim": 128, "heads": heads, "kv_heads": kv_heads, "vdim": vdim},
+             "mlp": {"ff": ff, "kind": "dense", "limit": 7.0}}
+    return {"architecture": "Dugazen", "layers": [att if i % 2 == 0 else delta for i in range(layers)], "logit_scale": 1.0,
+            "norm": {"eps": 1e-6}, "residual_mult": 1.0, "vocab": vocab, "width": width}
+
+
+DESIGN_SIZES = {     # name: (width, layers, heads, kv heads, feed-forward, vocab)
+    "2048x16": (2048, 16, 16, 8, 6144, 151936),
+    "4096x8": (4096, 8, 32, 8, 12288, 151936),
+}
+
+
+def design_bench(args) -> dict:
+    """Prefill (one prompt of --prefill-tokens in one step) and decode (--batch requests ending at --context)
+    throughput of Dugazen and of Qwen3 with the same width, layer count, heads and feed-forward, random bfloat16
+    weights, device time by CUDA events. With --profile the steps of one kind run between cudaProfilerStart/Stop."""
+    import numpy as np
+    import torch
+    from tiny_inference_engine_b200 import SamplingParams, StepEntry, StepRunner, load_model, make_cache
+    B, CTX, T, K, W = args.batch, min(args.context, 4096), args.prefill_tokens, min(args.steps, 64), max(args.warmup, 3)
+    rng = np.random.default_rng(0)
+    clocks = ClockSampler()
+    clocks.start()
+    rows = []
+    for size in ([args.design_size] if args.design_size else list(DESIGN_SIZES)):
+        width, layers, heads, kv_heads, ff, vocab = DESIGN_SIZES[size]
+        if args.layers:
+            layers = args.layers
+        configs = {"dugazen": dugazen_config(width, layers, heads, kv_heads, ff, vocab, vdim=args.design_vdim),
+                   "qwen3": dict(QWEN3_8B, hidden_size=width, intermediate_size=ff, num_hidden_layers=layers,
+                                 num_attention_heads=heads, num_key_value_heads=kv_heads, vocab_size=vocab)}
+        row = {"size": size, "layers": layers, "width": width, "heads": heads, "kv_heads": kv_heads, "ff": ff}
+        for name, config in configs.items():
+            if args.design_only and name != args.design_only:
+                continue
+            with tempfile.TemporaryDirectory() as d:
+                (Path(d) / "config.json").write_text(json.dumps(config))
+                model = load_model(d, "bfloat16", random_weights=True, seed=0)
+            pages = B * (CTX // PAGE + 2) + T // PAGE + 8
+            cache, states = make_cache(model, page_size=PAGE, num_pages=pages, max_requests=B + 2)
+            runner = StepRunner(model, cache, max_tokens=T, max_seqs=B, max_logit_rows=B, states=states,
+                                use_graphs=args.profile is None)
+
+            def prefill_once():
+                req = cache.new_request()
+                cache.reserve(req, T)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                e0.record()
+                runner.run([StepEntry(req, rng.integers(0, vocab, T), 0, [T - 1])])
+                e1.record()
+                torch.cuda.synchronize()
+                cache.release(req)
+                return e0.elapsed_time(e1)
+
+            def decode(steps, warmup, profile=False):
+                start = CTX - steps - warmup
+                reqs = []
+                for _ in range(B):
+                    req = cache.new_request()
+                    assert cache.reserve(req, CTX)
+                    toks = rng.integers(0, vocab, start)
+                    for at in range(0, start, T):
+                        runner.run([StepEntry(req, toks[at:at + T], at, [])])
+                        cache.advance_window(req, min(at + T, start))
+                    reqs.append(req)
+                greedy = [(SamplingParams(), 0)] * B
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                for i in range(steps + warmup):
+                    if i == warmup:
+                        torch.cuda.synchronize()
+                        if profile:
+                            torch.cuda.profiler.start()
+                        e0.record()
+                    runner.run([StepEntry(r, [int(rng.integers(0, vocab))], start + i, [0]) for r in reqs], greedy)
+                e1.record()
+                torch.cuda.synchronize()
+                if profile:
+                    torch.cuda.profiler.stop()
+                for r in reqs:
+                    cache.release(r)
+                return e0.elapsed_time(e1) / steps
+
+            if args.profile == "prefill":
+                prefill_once()
+                torch.cuda.profiler.start()
+                prefill_once()
+                torch.cuda.profiler.stop()
+            elif args.profile == "decode":
+                decode(2, 2, profile=True)
+            else:
+                for _ in range(3):
+                    prefill_once()
+                pre = sorted(prefill_once() for _ in range(5))[2]
+                ms = decode(K, W)
+                row[name] = {"prefill_tok_s": round(T / (pre / 1e3), 1), "prefill_ms": round(pre, 3),
+                             "decode_tok_s": round(B / (ms / 1e3), 1), "decode_ms_per_step": round(ms, 4)}
+            runner.check()
+            del runner, cache, states, model
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+        rows.append(row)
+    return {"design": "dugazen", "beside": "qwen3 at equal width, layers, heads and feed-forward", "dtype": "bf16",
+            "data": "synthetic (random weights, uniform random token ids)", "prefill_tokens": T, "batch": B, "context": CTX,
+            "value_head": args.design_vdim, "window": 1024, "sizes": rows, "clocks": clocks.stop()}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -198,8 +313,21 @@ def main() -> int:
     ap.add_argument("--profile", choices=["decode", "prefill", "mixed"], help="run two steps of one kind (mixed: 30 requests "
                     "decoding at context 2,048 beside a 482-token portion of a prompt, the serving default of 512 tokens a step), kernel by kernel, between "
                     "cudaProfilerStart/Stop (for ncu --profile-from-start off) and print no bench line")
+    ap.add_argument("--design", choices=["dugazen"], help="prefill and decode throughput of that design beside Qwen3 at equal "
+                    "sizes (a line of its own; the default workload and its line stay as they are)")
+    ap.add_argument("--design-size", choices=sorted(DESIGN_SIZES), help="--design: one size only")
+    ap.add_argument("--design-vdim", type=int, default=128, help="--design: size of a value head (keys have 128)")
+    ap.add_argument("--design-only", choices=["dugazen", "qwen3"], help="--design: one of the two models only")
     args = ap.parse_args()
 
+    if args.design:
+        if args.profile == "mixed":
+            print("bench.py --design profiles prefill or decode steps")
+            return 2
+        out = design_bench(args)
+        if args.profile is None:
+            print(json.dumps(out))
+        return 0
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a C++/Objective-C++ CMake project with a "
                           "Metal GPU backend (Apple only); pip cannot install it (no setup.py or pyproject.toml) and it has no CUDA path"}))

@@ -24,8 +24,11 @@ ODD = plain.make_config([D(heads=3, kv_heads=1, dim=40, vdim=20, conv=2), D(head
 ONES = plain.make_config([A(heads=1, kv_heads=1, dim=8, vdim=8, window=1, rot_dims=8), D(heads=1, kv_heads=1, dim=8, vdim=8, conv=5),
                           A(heads=1, kv_heads=1, dim=8, vdim=8, window=1000, rot_dims=4)], vocab=33, width=16,
                          residual_mult=1.0, logit_scale=1.0)
+# keys and values of one size that the tensor-core attention kernels take (bfloat16 runs there)
+SQUARE = plain.make_config([A(heads=4, kv_heads=2, dim=64, vdim=64, window=40, rot_dims=32), D(),
+                            A(heads=4, kv_heads=2, dim=64, vdim=64, window=300, rot_dims=64, ff=None)], width=64)
 CONFIGS = {"mixed": (MIXED, dict(low_rank=8, gate_rank=5), 16), "odd": (ODD, dict(low_rank=3, gate_rank=16), 8),
-           "ones": (ONES, dict(low_rank=1, gate_rank=2), 4)}
+           "ones": (ONES, dict(low_rank=1, gate_rank=2), 4), "square": (SQUARE, dict(low_rank=8, gate_rank=8), 16)}
 class Want:
     """The plain implementation's logits, and how far the same implementation moves when its activations are
     rounded to bfloat16 (largest difference of a row relative to its largest logit, worst row)."""
@@ -129,6 +132,7 @@ def truth():
 SINGLE = {
     "attention": plain.make_config([A(ff=None, v_mix=False)]),
     "attention_full_rotation_no_window_in_reach": plain.make_config([A(ff=None, rot_dims=32, window=500, v_mix=False)]),
+    "attention_heads_of_one_size": plain.make_config([A(heads=4, kv_heads=1, dim=128, vdim=128, window=30, rot_dims=64, ff=None, v_mix=False)]),
     "value_blend": plain.make_config([A(ff=None), A(ff=None, v_mix=False), A(ff=None)]),
     "delta": plain.make_config([D()]),
     "delta_one_tap_heads_alike": plain.make_config([D(heads=2, kv_heads=2, conv=1)]),
@@ -184,7 +188,7 @@ def test_whole_prompts_decoding_and_portions(tmp_path, truth, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mixed", "odd"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "square"])
 def test_mixed_batches_on_a_small_pool_with_two_state_slots(tmp_path, truth, name, dtype):
     """Requests of unequal lengths, portions of some beside single tokens of others, never more than two alive:
     pages and state slots are given back and used again, and every row equals the request run alone."""
@@ -231,18 +235,18 @@ def _mark_a_token(w, cfg, marked, seed):
     return d
 
 
-def _peaked_attention(window, at):
+def _peaked_attention(window, at, dim=16, vdim=24):
     """One attention layer in which the key of the token at place `at` gets a score far above all others from every
-    query while it is in the window: key dimension 15 (outside the rotated ones) answers to that token alone, and
+    query while it is in the window: the last key dimension (outside the rotated ones) answers to that token alone, and
     every query has a large entry there."""
-    cfg = plain.make_config([A(heads=2, kv_heads=1, dim=16, vdim=24, window=window, rot_dims=4, v_mix=False, ff=None, scale=1.0)],
+    cfg = plain.make_config([A(heads=2, kv_heads=1, dim=dim, vdim=vdim, window=window, rot_dims=4, v_mix=False, ff=None, scale=1.0)],
                             vocab=40, width=32, logit_scale=1.0)
     w = plain.random_weights(cfg, 8, sharp=1.0)
     marked = 7
     d = _mark_a_token(w, cfg, marked, 1)
-    w["l0.mix.k"][15] = 0.5 * d
+    w["l0.mix.k"][dim - 1] = 0.5 * d
     w["l0.mix.k.b"][:] = 0.0
-    w["l0.mix.q.b"][15] = w["l0.mix.q.b"][31] = 6.0
+    w["l0.mix.q.b"][dim - 1] = w["l0.mix.q.b"][2 * dim - 1] = 6.0 * (dim / 16) ** 0.5
     w["l0.mix.q.norm"][:] = 1.0
     w["l0.mix.k.norm"][:] = 4.0
     w["l0.mix.v"] = plain.round_bf16(w["l0.mix.v"] * 4.0)
@@ -252,12 +256,13 @@ def _peaked_attention(window, at):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_a_key_just_inside_and_just_outside_the_window(tmp_path, dtype):
+@pytest.mark.parametrize("sizes", [(16, 24), (64, 64)])       # the second pair runs on the tensor cores in bfloat16
+def test_a_key_just_inside_and_just_outside_the_window(tmp_path, dtype, sizes):
     """A key that dominates every score while it is seen: the rows where it is the window's oldest key and the
     rows right after it left differ visibly, in a prompt, in portions cut at the edge, and token by token, with
     the key on a page's border."""
     window, at = 21, 31                                   # page 8: the key is a page's last slot; page 16: its 16th
-    cfg, w, toks = _peaked_attention(window, at)
+    cfg, w, toks = _peaked_attention(window, at, *sizes)
     ref = reference(w, cfg, toks)
     want = ref.rows
     last_in, first_out = at + window - 1, at + window

@@ -44,6 +44,7 @@ struct DecodeArgs {
   int* status;
   long long q_stride;
   int max_blocks, q_heads, kv_heads, page_size, page_shift, window, split_keys, max_splits;
+  int exact_weights;     // != 0: the softmax weights enter the value product as two bfloat16 terms (pv_tile)
   float scale_log2;
   // Only for the kernel that prepares its heads itself (PREP): the output of the q/k/v product, [T, (q_heads + 2 kv_heads)
   // * head_dim] as bfloat16 rows (qkv) or as `part_splits` float partial sums (part + z * part_stride + t * part_ld + column),
@@ -297,7 +298,7 @@ __global__ void __launch_bounds__(kDecThreads) attn_decode_tma_kernel(const __gr
           }
         }
         softmax_update<DH, 2>(sc, m, l, acc);
-        pv_tile<DH, 2, L>(acc, sc, k_tile + PLANE_BYTES, warp * 16);
+        pv_tile<DH, 2, L>(acc, sc, k_tile + PLANE_BYTES, warp * 16, a.exact_weights != 0);
       }
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(empty + s)) : "memory");
@@ -591,12 +592,11 @@ TIE_API int tie_attention_decode_limit(int which) { return which == 0 ? kMaxTabl
 // launch (the kernel leaves them zero). pages is the number of pages of the cache planes. cluster != 0: the splits of
 // a sequence and kv head run as one thread-block cluster and merge through shared memory (max_splits 2, 4, 8 or 16;
 // scratch and counters are not touched); worth it where all n_list * kv_heads * max_splits CTAs are resident at once.
-TIE_API int tie_attention_decode_tma(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,
-                                     const int* query_start, const int* context_lens, const int* block_tables,
-                                     int max_blocks, int q_heads, int kv_heads, int head_dim, int page_size, int pages,
-                                     int window, float scale, const int* seq_list, int seq_first, int n_list,
-                                     int split_keys,
-                                     int max_splits, float* scratch, int* counters, int cluster, cudaStream_t s) {
+static int decode_tma_plain(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,
+                            const int* query_start, const int* context_lens, const int* block_tables, int max_blocks,
+                            int q_heads, int kv_heads, int head_dim, int page_size, int pages, int window, float scale,
+                            const int* seq_list, int seq_first, int n_list, int split_keys, int max_splits, float* scratch,
+                            int* counters, int cluster, int exact_weights, cudaStream_t s) {
   TIE_REQUIRE(q_stride % 8 == 0 && reinterpret_cast<uintptr_t>(q) % 16 == 0, "attention_decode: q rows must be 16-byte aligned");
   DecodeArgs a{};
   a.q = static_cast<const __nv_bfloat16*>(q);
@@ -604,8 +604,31 @@ TIE_API int tie_attention_decode_tma(const void* q, long long q_stride, const vo
   a.query_start = query_start, a.context_lens = context_lens, a.block_tables = block_tables, a.seq_list = seq_list, a.seq_first = seq_first;
   a.scratch = scratch, a.counters = counters, a.q_stride = q_stride;
   a.max_blocks = max_blocks, a.q_heads = q_heads, a.kv_heads = kv_heads, a.page_size = page_size, a.window = window;
-  a.split_keys = split_keys, a.max_splits = max_splits;
+  a.split_keys = split_keys, a.max_splits = max_splits, a.exact_weights = exact_weights;
   return decode_tma(a, false, cluster != 0, k_cache, v_cache, head_dim, pages, n_list, scale, s);
+}
+
+TIE_API int tie_attention_decode_tma(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,
+                                     const int* query_start, const int* context_lens, const int* block_tables,
+                                     int max_blocks, int q_heads, int kv_heads, int head_dim, int page_size, int pages,
+                                     int window, float scale, const int* seq_list, int seq_first, int n_list,
+                                     int split_keys,
+                                     int max_splits, float* scratch, int* counters, int cluster, cudaStream_t s) {
+  return decode_tma_plain(q, q_stride, k_cache, v_cache, out, query_start, context_lens, block_tables, max_blocks, q_heads, kv_heads,
+                          head_dim, page_size, pages, window, scale, seq_list, seq_first, n_list, split_keys, max_splits, scratch,
+                          counters, cluster, 0, s);
+}
+
+// The same with the softmax weights kept to 16 bits of mantissa in the value product (two MMAs a tile).
+TIE_API int tie_attention_decode_tma_exact(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,
+                                           const int* query_start, const int* context_lens, const int* block_tables,
+                                           int max_blocks, int q_heads, int kv_heads, int head_dim, int page_size, int pages,
+                                           int window, float scale, const int* seq_list, int seq_first, int n_list,
+                                           int split_keys, int max_splits, float* scratch, int* counters, int cluster,
+                                           cudaStream_t s) {
+  return decode_tma_plain(q, q_stride, k_cache, v_cache, out, query_start, context_lens, block_tables, max_blocks, q_heads, kv_heads,
+                          head_dim, page_size, pages, window, scale, seq_list, seq_first, n_list, split_keys, max_splits, scratch,
+                          counters, cluster, 1, s);
 }
 
 // The same attention for a step in which every sequence brings one token, straight from the output of the q/k/v

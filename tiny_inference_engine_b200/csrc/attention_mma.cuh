@@ -100,17 +100,32 @@ __device__ __forceinline__ void qk_tile(float (&s)[NT][4], const uint32_t (&qf)[
   }
 }
 
+// What rounding (lo, hi) to the bfloat16 pair `packed` left over, itself as a bfloat16 pair.
+__device__ __forceinline__ uint32_t pack_bf16_rest(float lo, float hi, uint32_t packed) {
+  const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&packed);
+  return pack_bf16(lo - __low2float(h), hi - __high2float(h));
+}
+
 // acc[16 x DH] += P[16 x (8 * NT)] . V for the NT * 8 keys starting at row `key_row` of the V tile.
+// `exact`: the float weights enter the product as two bfloat16 terms, p = hi + lo (16 bits of mantissa instead of
+// 8, an error of 2^-17 of a weight), each with an MMA of its own: for models that ask for softmax weights in 32-bit.
 template <int DH, int NT, typename L = RowLayout<DH>>
-__device__ __forceinline__ void pv_tile(float (&acc)[DH / 8][4], const float (&p)[NT][4], uint32_t v_tile, int key_row) {
+__device__ __forceinline__ void pv_tile(float (&acc)[DH / 8][4], const float (&p)[NT][4], uint32_t v_tile, int key_row,
+                                        bool exact = false) {
   const int lane = threadIdx.x & 31;
 #pragma unroll
   for (int kk = 0; kk < NT / 2; ++kk) {     // 16 keys per MMA k-step
-    uint32_t a[4];
+    uint32_t a[4], rest[4] = {0u, 0u, 0u, 0u};
     a[0] = pack_bf16(p[2 * kk][0], p[2 * kk][1]);
     a[1] = pack_bf16(p[2 * kk][2], p[2 * kk][3]);
     a[2] = pack_bf16(p[2 * kk + 1][0], p[2 * kk + 1][1]);
     a[3] = pack_bf16(p[2 * kk + 1][2], p[2 * kk + 1][3]);
+    if (exact) {
+      rest[0] = pack_bf16_rest(p[2 * kk][0], p[2 * kk][1], a[0]);
+      rest[1] = pack_bf16_rest(p[2 * kk][2], p[2 * kk][3], a[1]);
+      rest[2] = pack_bf16_rest(p[2 * kk + 1][0], p[2 * kk + 1][1], a[2]);
+      rest[3] = pack_bf16_rest(p[2 * kk + 1][2], p[2 * kk + 1][3], a[3]);
+    }
 #pragma unroll
     for (int dp = 0; dp < DH / 16; ++dp) {  // two output tiles of 8 dims per ldmatrix.x4.trans
       uint32_t b[4];
@@ -119,6 +134,10 @@ __device__ __forceinline__ void pv_tile(float (&acc)[DH / 8][4], const float (&p
       ldmatrix_x4_trans(b, v_tile + L::at(r, c));
       mma_bf16(acc[2 * dp], a, b[0], b[1]);
       mma_bf16(acc[2 * dp + 1], a, b[2], b[3]);
+      if (exact) {
+        mma_bf16(acc[2 * dp], rest, b[0], b[1]);
+        mma_bf16(acc[2 * dp + 1], rest, b[2], b[3]);
+      }
     }
   }
 }

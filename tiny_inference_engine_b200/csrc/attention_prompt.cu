@@ -31,6 +31,7 @@ struct PromptArgs {
   long long q_stride;
   int max_blocks, q_heads, kv_heads, page_size, page_shift, window;
   float scale_log2;
+  int exact_weights;      // != 0: the softmax weights enter the value product as two bfloat16 terms (pv_tile)
 };
 
 template <int DH, int STAGES>
@@ -170,7 +171,7 @@ __global__ void __launch_bounds__(kPromptThreads) attn_prompt_tma_kernel(const _
           }
         }
         softmax_update<DH, 8>(sc, m, l, acc);
-        pv_tile<DH, 8, L>(acc, sc, k_tile + PLANE_BYTES, 0);
+        pv_tile<DH, 8, L>(acc, sc, k_tile + PLANE_BYTES, 0, a.exact_weights != 0);
       }
       __syncwarp();
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(empty + s)) : "memory");
@@ -221,10 +222,10 @@ using namespace tie;
 // Rows [0, rows) of the step belong to sequences 0..n_seqs-1, each bringing several tokens;
 // max_queries is the largest number of tokens one of them brings; pages is the number of pages
 // of the cache planes.
-TIE_API int tie_attention_prompt_tma(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,
-                                     const int* query_start, const int* context_lens, const int* block_tables,
-                                     int max_blocks, int n_seqs, int max_queries, int q_heads, int kv_heads, int head_dim,
-                                     int page_size, int pages, int window, float scale, cudaStream_t s) {
+static int prompt_tma(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,
+                      const int* query_start, const int* context_lens, const int* block_tables, int max_blocks, int n_seqs,
+                      int max_queries, int q_heads, int kv_heads, int head_dim, int page_size, int pages, int window,
+                      float scale, int exact_weights, cudaStream_t s) {
   TIE_REQUIRE(head_dim == 64 || head_dim == 128 || head_dim == 256, "attention_prompt: head_dim %d is not 64, 128 or 256", head_dim);
   TIE_REQUIRE(q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && q_heads / kv_heads <= 16,
               "attention_prompt: %d query heads over %d kv heads (at most 16 per group)", q_heads, kv_heads);
@@ -242,7 +243,8 @@ TIE_API int tie_attention_prompt_tma(const void* q, long long q_stride, const vo
               "attention_prompt: cuTensorMapEncodeTiled failed");
   TIE_REQUIRE(status_word() != nullptr, "attention_prompt: cannot allocate the status word");
   PromptArgs a{static_cast<const __nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(out), query_start, context_lens, block_tables,
-               status_word(), q_stride, max_blocks, q_heads, kv_heads, page_size, shift, window, scale * 1.4426950408889634f};
+               status_word(), q_stride, max_blocks, q_heads, kv_heads, page_size, shift, window, scale * 1.4426950408889634f,
+               exact_weights};
   const int max_rows = max_queries * (q_heads / kv_heads);
   int st = kOk;
   if (head_dim == 64) st = launch_prompt_tma<64>(km, vm, a, n_seqs, max_rows, s);
@@ -250,4 +252,21 @@ TIE_API int tie_attention_prompt_tma(const void* q, long long q_stride, const vo
   else st = launch_prompt_tma<256>(km, vm, a, n_seqs, max_rows, s);
   if (st != kOk) return st;
   TIE_RETURN_LAUNCH("attention_prompt_tma");
+}
+
+TIE_API int tie_attention_prompt_tma(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,
+                                     const int* query_start, const int* context_lens, const int* block_tables,
+                                     int max_blocks, int n_seqs, int max_queries, int q_heads, int kv_heads, int head_dim,
+                                     int page_size, int pages, int window, float scale, cudaStream_t s) {
+  return prompt_tma(q, q_stride, k_cache, v_cache, out, query_start, context_lens, block_tables, max_blocks, n_seqs, max_queries,
+                    q_heads, kv_heads, head_dim, page_size, pages, window, scale, 0, s);
+}
+
+// The same with the softmax weights kept to 16 bits of mantissa in the value product (two MMAs a tile).
+TIE_API int tie_attention_prompt_tma_exact(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out,
+                                           const int* query_start, const int* context_lens, const int* block_tables,
+                                           int max_blocks, int n_seqs, int max_queries, int q_heads, int kv_heads,
+                                           int head_dim, int page_size, int pages, int window, float scale, cudaStream_t s) {
+  return prompt_tma(q, q_stride, k_cache, v_cache, out, query_start, context_lens, block_tables, max_blocks, n_seqs, max_queries,
+                    q_heads, kv_heads, head_dim, page_size, pages, window, scale, 1, s);
 }

@@ -9,12 +9,14 @@
 // per key channel. Columns of S do not depend on one another, so the work is cut by (sequence, head, columns).
 //
 // Three kernels, all of them float inside:
-//   delta_prep   one block per token: convolution (its first taps - 1 inputs come from the sequence's state slot or
-//                from the rows ahead of it in the step) + SiLU, unit norm of q and k per head, sigmoid of beta.
+//   delta_prep   one block per (token, head of q, k or v): convolution (its first taps - 1 inputs come from the
+//                sequence's state slot or from the rows ahead of it in the step) + SiLU, unit norm of q and k per
+//                head; further blocks turn the raw decay projection into decays (in place) and take beta's sigmoid.
 //   delta_rule   one block per (sequence, head, 16 columns): the recurrence over the sequence's tokens of the
-//                step, state read from and written back to the slot. Eight lanes share a column, each holding
-//                every eighth key channel; decays are worked out while a chunk of tokens is staged in shared
-//                memory. The block of head 0, columns 0 also moves the convolution's last inputs into the slot.
+//                step, state read from and written back to the slot in row pieces through shared memory. Eight
+//                lanes share a column, each holding every eighth key channel; a chunk of tokens is staged in shared
+//                memory at a time. The block of head 0, columns 0 also moves the convolution's last inputs into
+//                the slot.
 //   delta_out    one warp per (token, head): o / rms(o) * w * sigmoid(gate).
 //
 // A state slot is one float row: S of every head [heads, dim, vdim], then the convolution's last taps - 1
@@ -34,6 +36,9 @@ __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
 
 // proj row: q at q_off [kv_heads * dim], k at k_off, v at v_off [heads * vdim], beta at b_off [heads].
+// One block per (token, unit). Units: the q heads, the k heads, the v heads (convolution + SiLU over the unit's
+// channels; q and k also their unit norm), then one unit per head that turns the raw decay projection into decays
+// in place, and a last one for beta.
 template <typename T>
 __global__ void __launch_bounds__(128) delta_prep_kernel(const T* __restrict__ proj, long long stride, int q_off, int k_off,
                                                          int v_off, int b_off, const float* __restrict__ conv_w,
@@ -42,17 +47,40 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(const T* __restrict__ p
                                                          const int* __restrict__ query_start,
                                                          const int* __restrict__ state_slots, DeltaShape sh, float unit_eps,
                                                          float q_scale, float* __restrict__ qn, float* __restrict__ kn,
-                                                         float* __restrict__ vn, float* __restrict__ beta) {
+                                                         float* __restrict__ vn, float* __restrict__ beta,
+                                                         float* __restrict__ decay, long long decay_stride,
+                                                         const float* __restrict__ dt_bias, const float* __restrict__ a_log) {
   pdl_sync();
-  extern __shared__ float buf[];     // the convolved q and k of this token
-  const int t = blockIdx.x;
+  __shared__ float scratch[33];
+  const int t = blockIdx.x, unit = blockIdx.y;
+  const int G = sh.kv_heads, H = sh.heads, dim = sh.dim, vdim = sh.vdim, taps = sh.taps;
+  const int nqk = G * dim, nv = H * vdim, C = 2 * nqk + nv;
+  const T* row = proj + static_cast<long long>(t) * stride;
+  if (unit == 2 * G + 2 * H) {
+    for (int h = threadIdx.x; h < H; h += blockDim.x) beta[static_cast<long long>(t) * H + h] = sigmoidf_(ld(row + b_off + h));
+    return;
+  }
+  if (unit >= 2 * G + H) {            // decay = exp(-rate * softplus(raw + bias)), in place
+    const int h = unit - (2 * G + H);
+    const float rate = expf(a_log[h]);
+    float* a = decay + static_cast<long long>(t) * decay_stride + h * dim;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) a[d] = expf(-rate * softplusf_(a[d] + dt_bias[h * dim + d]));
+    return;
+  }
   const int s = seq_of_row[t];
   const int j = t - query_start[s];          // tokens of this sequence ahead of this one in the step
   const int slot = state_slots[s];
-  const int nqk = sh.kv_heads * sh.dim, nv = sh.heads * sh.vdim, C = 2 * nqk + nv, taps = sh.taps;
   const float* tail = slot >= 0 ? state + slot * state_stride + conv_state_off : nullptr;
-  const T* row = proj + static_cast<long long>(t) * stride;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  const bool is_v = unit >= 2 * G;
+  const int width = is_v ? vdim : dim;
+  const int c0 = is_v ? 2 * nqk + (unit - 2 * G) * vdim : unit * dim;      // the unit's first channel of all C
+  float* dst = is_v ? vn + static_cast<long long>(t) * nv + (unit - 2 * G) * vdim
+                    : (unit < G ? qn + static_cast<long long>(t) * nqk + unit * dim
+                                : kn + static_cast<long long>(t) * nqk + (unit - G) * dim);
+  float vals[2] = {0.0f, 0.0f};              // dim <= 256: at most two channels of a q or k head per thread
+  float ss = 0.0f;
+  for (int d = threadIdx.x, n = 0; d < width; d += blockDim.x, ++n) {
+    const int c = c0 + d;
     const int col = c < nqk ? q_off + c : (c < 2 * nqk ? k_off + (c - nqk) : v_off + (c - 2 * nqk));
     float y = 0.0f;
     for (int i = 0; i < taps; ++i) {
@@ -63,35 +91,35 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(const T* __restrict__ p
       y = fmaf(conv_w[c * taps + i], in, y);
     }
     y = y * sigmoidf_(y);
-    if (c < 2 * nqk) buf[c] = y;
-    else vn[static_cast<long long>(t) * nv + (c - 2 * nqk)] = y;
+    if (is_v) {
+      dst[d] = y;
+    } else {
+      if (n < 2) vals[n] = y;
+      ss += y * y;
+    }
   }
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  for (int h = warp; h < 2 * sh.kv_heads; h += warps) {    // q heads, then k heads
-    const float* x = buf + h * sh.dim;
-    float ss = 0.0f;
-    for (int d = lane; d < sh.dim; d += 32) ss += x[d] * x[d];
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss + unit_eps);
-    const bool is_q = h < sh.kv_heads;
-    float* dst = (is_q ? qn : kn) + static_cast<long long>(t) * nqk + (is_q ? h : h - sh.kv_heads) * sh.dim;
-    for (int d = lane; d < sh.dim; d += 32) dst[d] = is_q ? (x[d] * inv) * q_scale : x[d] * inv;
-  }
-  for (int h = threadIdx.x; h < sh.heads; h += blockDim.x) beta[static_cast<long long>(t) * sh.heads + h] = sigmoidf_(ld(row + b_off + h));
+  if (is_v) return;
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss + unit_eps);
+  for (int d = threadIdx.x, n = 0; d < width && n < 2; d += blockDim.x, ++n) dst[d] = unit < G ? (vals[n] * inv) * q_scale : vals[n] * inv;
 }
 
 constexpr int kDeltaLanes = 8;       // lanes that share a column of S
 constexpr int kDeltaCols = 16;       // columns of a block (128 threads)
+constexpr int kDeltaPad = kDeltaCols + 1;
 
+// One block per (sequence, head, 16 columns of S). A column's key channels are spread over eight lanes (lane i
+// holds channels i, i + 8, ...), so a token costs one pass over the registers with two dot products (against k and
+// against q of the decayed state), three shuffle steps for both, and the update: with d1 = (gS)^T k and
+// d2 = (gS)^T q, u = beta (v - d1) and the read-out of the updated state is o = d2 + (k . q) u.
 // RMAX: key channels a lane may hold (dim <= 8 * RMAX).
 template <typename T, int RMAX>
 __global__ void __launch_bounds__(kDeltaLanes * kDeltaCols) delta_rule_kernel(
     const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vn, const float* __restrict__ beta,
-    const float* __restrict__ a_raw, long long a_stride, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
-    float* __restrict__ state, long long state_stride, long long conv_state_off, const T* __restrict__ proj,
-    long long proj_stride, int q_off, int k_off, int v_off, const int* __restrict__ query_start,
-    const int* __restrict__ state_slots, DeltaShape sh, int chunk, float* __restrict__ out) {
+    const float* __restrict__ decay, long long decay_stride, float* __restrict__ state, long long state_stride,
+    long long conv_state_off, const T* __restrict__ proj, long long proj_stride, int q_off, int k_off, int v_off,
+    const int* __restrict__ query_start, const int* __restrict__ state_slots, DeltaShape sh, int chunk,
+    float* __restrict__ out) {
   pdl_sync();
   extern __shared__ float smem[];
   const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kDeltaCols;
@@ -100,21 +128,29 @@ __global__ void __launch_bounds__(kDeltaLanes * kDeltaCols) delta_rule_kernel(
   const int t0 = query_start[s], n = query_start[s + 1] - t0;
   const int dim = sh.dim, vdim = sh.vdim, nqk = sh.kv_heads * dim, nv = sh.heads * vdim;
   const int g = h / (sh.heads / sh.kv_heads);
-  const int lane8 = threadIdx.x % kDeltaLanes, col = col0 + threadIdx.x / kDeltaLanes;
+  const int lane8 = threadIdx.x % kDeltaLanes, cidx = threadIdx.x / kDeltaLanes, col = col0 + cidx;
   const bool live = col < vdim;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float* S = state + slot * state_stride + static_cast<long long>(h) * dim * vdim;
+  // The block's 16 columns of S come in row pieces of 64 bytes through shared memory (the lanes' own elements
+  // are a row apart in memory).
+  for (int i = threadIdx.x; i < dim * kDeltaCols; i += blockDim.x) {
+    const int r = i / kDeltaCols, c = i % kDeltaCols;
+    smem[r * kDeltaPad + c] = col0 + c < vdim ? S[static_cast<long long>(r) * vdim + col0 + c] : 0.0f;
+  }
+  __syncthreads();
   float sreg[RMAX];
 #pragma unroll
   for (int r = 0; r < RMAX; ++r) {
     const int rowi = lane8 + kDeltaLanes * r;
-    sreg[r] = (live && rowi < dim) ? S[static_cast<long long>(rowi) * vdim + col] : 0.0f;
+    sreg[r] = rowi < dim ? smem[rowi * kDeltaPad + cidx] : 0.0f;
   }
-  float* kb = smem;                           // [chunk][dim]
+  float* kb = smem;                           // [chunk][dim]   (the staging tile above is done with)
   float* qb = kb + chunk * dim;
   float* gb = qb + chunk * dim;               // decays
   float* vb = gb + chunk * dim;               // [chunk][kDeltaCols]
-  float* bb = vb + chunk * kDeltaCols;        // [chunk]
-  const float rate = expf(a_log[h]);
+  float* bb = vb + chunk * kDeltaCols;        // [chunk] beta
+  float* kq = bb + chunk;                     // [chunk] k . q
   for (int c0 = 0; c0 < n; c0 += chunk) {
     const int cn = min(chunk, n - c0);
     __syncthreads();
@@ -123,8 +159,7 @@ __global__ void __launch_bounds__(kDeltaLanes * kDeltaCols) delta_rule_kernel(
       const long long t = t0 + c0 + tc;
       kb[i] = kn[t * nqk + g * dim + d];
       qb[i] = qn[t * nqk + g * dim + d];
-      const float step = softplusf_(a_raw[t * a_stride + h * dim + d] + dt_bias[h * dim + d]);
-      gb[i] = expf(-rate * step);
+      gb[i] = decay[t * decay_stride + h * dim + d];
     }
     for (int i = threadIdx.x; i < cn * kDeltaCols; i += blockDim.x) {
       const int tc = i / kDeltaCols, c = col0 + i % kDeltaCols;
@@ -132,44 +167,58 @@ __global__ void __launch_bounds__(kDeltaLanes * kDeltaCols) delta_rule_kernel(
     }
     for (int i = threadIdx.x; i < cn; i += blockDim.x) bb[i] = beta[(t0 + c0 + i) * static_cast<long long>(sh.heads) + h];
     __syncthreads();
+    for (int tc = warp; tc < cn; tc += (blockDim.x >> 5)) {
+      float d = 0.0f;
+      for (int e = lane; e < dim; e += 32) d = fmaf(kb[tc * dim + e], qb[tc * dim + e], d);
+      d = warp_sum(d);
+      if (lane == 0) kq[tc] = d;
+    }
+    __syncthreads();
     for (int tc = 0; tc < cn; ++tc) {
       const float* kt = kb + tc * dim;
       const float* qt = qb + tc * dim;
       const float* gt = gb + tc * dim;
-      float dot = 0.0f;
+      float d1a = 0.0f, d1b = 0.0f, d2a = 0.0f, d2b = 0.0f;
+#pragma unroll
+      for (int r = 0; r < RMAX; r += 2) {
+        const int ra = lane8 + kDeltaLanes * r, rb = ra + kDeltaLanes;
+        if (ra < dim) {
+          sreg[r] *= gt[ra];
+          d1a = fmaf(kt[ra], sreg[r], d1a);
+          d2a = fmaf(qt[ra], sreg[r], d2a);
+        }
+        if (rb < dim) {
+          sreg[r + 1] *= gt[rb];
+          d1b = fmaf(kt[rb], sreg[r + 1], d1b);
+          d2b = fmaf(qt[rb], sreg[r + 1], d2b);
+        }
+      }
+      float d1 = d1a + d1b, d2 = d2a + d2b;
+      d1 += __shfl_xor_sync(0xffffffffu, d1, 1);
+      d2 += __shfl_xor_sync(0xffffffffu, d2, 1);
+      d1 += __shfl_xor_sync(0xffffffffu, d1, 2);
+      d2 += __shfl_xor_sync(0xffffffffu, d2, 2);
+      d1 += __shfl_xor_sync(0xffffffffu, d1, 4);
+      d2 += __shfl_xor_sync(0xffffffffu, d2, 4);
+      const float u = bb[tc] * (vb[tc * kDeltaCols + cidx] - d1);
+      if (live && lane8 == 0) out[(t0 + c0 + tc) * static_cast<long long>(nv) + h * vdim + col] = fmaf(kq[tc], u, d2);
 #pragma unroll
       for (int r = 0; r < RMAX; ++r) {
         const int rowi = lane8 + kDeltaLanes * r;
-        if (rowi < dim) {
-          sreg[r] *= gt[rowi];
-          dot = fmaf(kt[rowi], sreg[r], dot);
-        }
+        if (rowi < dim) sreg[r] = fmaf(kt[rowi], u, sreg[r]);
       }
-      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-      dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-      const float u = bb[tc] * (vb[tc * kDeltaCols + threadIdx.x / kDeltaLanes] - dot);
-      float o = 0.0f;
-#pragma unroll
-      for (int r = 0; r < RMAX; ++r) {
-        const int rowi = lane8 + kDeltaLanes * r;
-        if (rowi < dim) {
-          sreg[r] = fmaf(kt[rowi], u, sreg[r]);
-          o = fmaf(qt[rowi], sreg[r], o);
-        }
-      }
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      o += __shfl_xor_sync(0xffffffffu, o, 4);
-      if (live && lane8 == 0) out[(t0 + c0 + tc) * static_cast<long long>(nv) + h * vdim + col] = o;
     }
   }
-  if (live) {
+  __syncthreads();
 #pragma unroll
-    for (int r = 0; r < RMAX; ++r) {
-      const int rowi = lane8 + kDeltaLanes * r;
-      if (rowi < dim) S[static_cast<long long>(rowi) * vdim + col] = sreg[r];
-    }
+  for (int r = 0; r < RMAX; ++r) {
+    const int rowi = lane8 + kDeltaLanes * r;
+    if (rowi < dim) smem[rowi * kDeltaPad + cidx] = sreg[r];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < dim * kDeltaCols; i += blockDim.x) {
+    const int r = i / kDeltaCols, c = i % kDeltaCols;
+    if (col0 + c < vdim) S[static_cast<long long>(r) * vdim + col0 + c] = smem[r * kDeltaPad + c];
   }
   // The convolution's last taps - 1 inputs after this step: from the step's rows where it brought enough,
   // else what the slot held moves up.
@@ -222,20 +271,22 @@ TIE_API int tie_delta_prep(int dtype, const void* proj, long long stride, int q_
                            const float* conv_w, const float* state, long long state_stride, long long conv_state_off,
                            const int* seq_of_row, const int* query_start, const int* state_slots, int tokens, int heads,
                            int kv_heads, int dim, int vdim, int taps, float unit_eps, float q_scale, float* qn, float* kn,
-                           float* vn, float* beta, cudaStream_t s) {
+                           float* vn, float* beta, float* decay, long long decay_stride, const float* dt_bias,
+                           const float* a_log, cudaStream_t s) {
   const DeltaShape sh{heads, kv_heads, dim, vdim, taps};
   if (const int st_ = check_delta(sh)) return st_;
   if (tokens <= 0) return kOk;
-  const size_t smem = static_cast<size_t>(2) * kv_heads * dim * sizeof(float);
-  TIE_REQUIRE(smem <= 48 * 1024, "delta_prep: q and k of %d values do not fit shared memory", 2 * kv_heads * dim);
+  const int units = 2 * kv_heads + 2 * heads + 1;
+  TIE_REQUIRE(units <= 65535, "delta_prep: %d heads exceed the grid", heads);
+  const dim3 grid(tokens, units);
   if (dtype == TIE_F32) {
-    TIE_LAUNCH((delta_prep_kernel<float>), tokens, 128, smem, s, static_cast<const float*>(proj), stride, q_off, k_off, v_off, b_off,
+    TIE_LAUNCH((delta_prep_kernel<float>), grid, 128, 0, s, static_cast<const float*>(proj), stride, q_off, k_off, v_off, b_off,
                conv_w, state, state_stride, conv_state_off, seq_of_row, query_start, state_slots, sh, unit_eps, q_scale, qn, kn,
-               vn, beta);
+               vn, beta, decay, decay_stride, dt_bias, a_log);
   } else if (dtype == TIE_BF16) {
-    TIE_LAUNCH((delta_prep_kernel<__nv_bfloat16>), tokens, 128, smem, s, static_cast<const __nv_bfloat16*>(proj), stride, q_off,
+    TIE_LAUNCH((delta_prep_kernel<__nv_bfloat16>), grid, 128, 0, s, static_cast<const __nv_bfloat16*>(proj), stride, q_off,
                k_off, v_off, b_off, conv_w, state, state_stride, conv_state_off, seq_of_row, query_start, state_slots, sh,
-               unit_eps, q_scale, qn, kn, vn, beta);
+               unit_eps, q_scale, qn, kn, vn, beta, decay, decay_stride, dt_bias, a_log);
   } else {
     set_error("unknown dtype code %d", dtype);
     return kBadArgument;
@@ -244,20 +295,22 @@ TIE_API int tie_delta_prep(int dtype, const void* proj, long long stride, int q_
 }
 
 template <typename T>
-static int launch_delta_rule(const float* qn, const float* kn, const float* vn, const float* beta, const float* a_raw,
-                             long long a_stride, const float* dt_bias, const float* a_log, float* state,
-                             long long state_stride, long long conv_state_off, const void* proj, long long proj_stride,
-                             int q_off, int k_off, int v_off, const int* query_start, const int* state_slots, int seqs,
-                             const DeltaShape& sh, float* out, cudaStream_t s) {
+static int launch_delta_rule(const float* qn, const float* kn, const float* vn, const float* beta, const float* decay,
+                             long long decay_stride, float* state, long long state_stride, long long conv_state_off,
+                             const void* proj, long long proj_stride, int q_off, int k_off, int v_off,
+                             const int* query_start, const int* state_slots, int seqs, const DeltaShape& sh, float* out,
+                             cudaStream_t s) {
   const dim3 grid(seqs, sh.heads, ceil_div(sh.vdim, kDeltaCols));
-  const int per_token = 3 * sh.dim + kDeltaCols + 1;
+  const int per_token = 3 * sh.dim + kDeltaCols + 2;
   int chunk = (40 * 1024 / static_cast<int>(sizeof(float))) / per_token;
   chunk = chunk > 32 ? 32 : (chunk < 1 ? 1 : chunk);
-  const size_t smem = static_cast<size_t>(chunk) * per_token * sizeof(float);
+  const int stage = sh.dim * kDeltaPad;                         // the state tile on its way in and out
+  const int floats = chunk * per_token > stage ? chunk * per_token : stage;
+  const size_t smem = static_cast<size_t>(floats) * sizeof(float);
   const T* p = static_cast<const T*>(proj);
 #define TIE_DELTA_CASE(R)                                                                                                  \
-  TIE_LAUNCH((delta_rule_kernel<T, R>), grid, kDeltaLanes * kDeltaCols, smem, s, qn, kn, vn, beta, a_raw, a_stride, dt_bias, a_log, \
-             state, state_stride, conv_state_off, p, proj_stride, q_off, k_off, v_off, query_start, state_slots, sh, chunk, out)
+  TIE_LAUNCH((delta_rule_kernel<T, R>), grid, kDeltaLanes * kDeltaCols, smem, s, qn, kn, vn, beta, decay, decay_stride, state, \
+             state_stride, conv_state_off, p, proj_stride, q_off, k_off, v_off, query_start, state_slots, sh, chunk, out)
   const int r = (sh.dim + kDeltaLanes - 1) / kDeltaLanes;
   if (r <= 2) TIE_DELTA_CASE(2);
   else if (r <= 4) TIE_DELTA_CASE(4);
@@ -269,20 +322,20 @@ static int launch_delta_rule(const float* qn, const float* kn, const float* vn, 
 }
 
 TIE_API int tie_delta_rule(int dtype, const float* qn, const float* kn, const float* vn, const float* beta,
-                           const float* a_raw, long long a_stride, const float* dt_bias, const float* a_log, float* state,
-                           long long state_stride, long long conv_state_off, const void* proj, long long proj_stride,
-                           int q_off, int k_off, int v_off, const int* query_start, const int* state_slots, int seqs,
-                           int heads, int kv_heads, int dim, int vdim, int taps, float* out, cudaStream_t s) {
+                           const float* decay, long long decay_stride, float* state, long long state_stride,
+                           long long conv_state_off, const void* proj, long long proj_stride, int q_off, int k_off,
+                           int v_off, const int* query_start, const int* state_slots, int seqs, int heads, int kv_heads,
+                           int dim, int vdim, int taps, float* out, cudaStream_t s) {
   const DeltaShape sh{heads, kv_heads, dim, vdim, taps};
   if (const int st_ = check_delta(sh)) return st_;
   if (seqs <= 0) return kOk;
   TIE_REQUIRE(seqs <= 65535 * 32 && heads <= 65535, "delta_rule: %d sequences x %d heads exceed the grid", seqs, heads);
   if (dtype == TIE_F32)
-    return launch_delta_rule<float>(qn, kn, vn, beta, a_raw, a_stride, dt_bias, a_log, state, state_stride, conv_state_off, proj,
-                                    proj_stride, q_off, k_off, v_off, query_start, state_slots, seqs, sh, out, s);
+    return launch_delta_rule<float>(qn, kn, vn, beta, decay, decay_stride, state, state_stride, conv_state_off, proj, proj_stride,
+                                    q_off, k_off, v_off, query_start, state_slots, seqs, sh, out, s);
   if (dtype == TIE_BF16)
-    return launch_delta_rule<__nv_bfloat16>(qn, kn, vn, beta, a_raw, a_stride, dt_bias, a_log, state, state_stride, conv_state_off,
-                                            proj, proj_stride, q_off, k_off, v_off, query_start, state_slots, seqs, sh, out, s);
+    return launch_delta_rule<__nv_bfloat16>(qn, kn, vn, beta, decay, decay_stride, state, state_stride, conv_state_off, proj,
+                                            proj_stride, q_off, k_off, v_off, query_start, state_slots, seqs, sh, out, s);
   set_error("unknown dtype code %d", dtype);
   return kBadArgument;
 }

@@ -14,7 +14,7 @@ namespace tie {
 
 // One block per output row. The row is kept in shared memory between the passes (dim floats).
 template <typename T>
-__global__ void __launch_bounds__(256) add_normed_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
+__global__ void __launch_bounds__(1024) add_normed_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
                                                                  const float* __restrict__ part, long long part_stride,
                                                                  int splits, const float* __restrict__ bias,
                                                                  const float* __restrict__ wb, float eps_b, float mult,
@@ -29,17 +29,31 @@ __global__ void __launch_bounds__(256) add_normed_rmsnorm_kernel(float* __restri
   const T* dr = delta ? delta + src : nullptr;
   const float* pr = part ? part + src : nullptr;
   float ss = 0.0f;
-  for (int k = threadIdx.x; k < dim; k += blockDim.x) {
-    float y;
+  const int nt = blockDim.x;
+  for (int k0 = threadIdx.x; k0 < dim; k0 += 4 * nt) {     // four elements a thread at a time, their loads in flight together
+    float y[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if (dr) {
-      y = ld(dr + k);
-    } else {
-      y = pr[k];
-      for (int z = 1; z < splits; ++z) y += pr[static_cast<long long>(z) * part_stride + k];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (k0 + i * nt < dim) y[i] = ld(dr + k0 + i * nt);
+    } else {                                                // split by split: each element still adds in split order
+#pragma unroll 4
+      for (int z = 0; z < splits; ++z) {
+        const float* pz = pr + static_cast<long long>(z) * part_stride;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (k0 + i * nt < dim) y[i] += pz[k0 + i * nt];
+      }
     }
-    if (bias) y += bias[k];
-    row[k] = y;
-    ss += y * y;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = k0 + i * nt;
+      if (k < dim) {
+        if (bias) y[i] += bias[k];
+        row[k] = y[i];
+        ss += y[i] * y[i];
+      }
+    }
   }
   ss = block_sum(ss, scratch);
   const float inv_y = 1.0f / sqrtf(ss / static_cast<float>(dim) + eps_b);
@@ -102,7 +116,7 @@ int launch_add_normed_rmsnorm(float* x, const void* delta, const float* part, lo
       return kBadArgument;
     }
   }
-  TIE_LAUNCH(kernel, n, dim >= 512 ? 256 : 128, smem, s, x, static_cast<const T*>(delta), part, part_stride, splits, bias, wb,
+  TIE_LAUNCH(kernel, n, dim >= 4096 ? 1024 : (dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128)), smem, s, x, static_cast<const T*>(delta), part, part_stride, splits, bias, wb,
              eps_b, mult, rows, w, eps, static_cast<T*>(out), dim);
   TIE_RETURN_LAUNCH("add_normed_rmsnorm");
 }

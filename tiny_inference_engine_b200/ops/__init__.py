@@ -322,11 +322,13 @@ def attention_decode_tma_takes(q: torch.Tensor, q_heads: int, kv_heads: int, hea
 
 
 def attention_prompt_tma(q, k_cache, v_cache, out, query_start, context_lens, block_tables, n_seqs: int, max_queries: int,
-                         q_heads, kv_heads, head_dim, scale: float, window: int = 0) -> None:
-    """As attention_prompt_tc, keys and values fed by TMA (pages that are powers of two from 8 up)."""
+                         q_heads, kv_heads, head_dim, scale: float, window: int = 0, exact_weights: bool = False) -> None:
+    """As attention_prompt_tc, keys and values fed by TMA (pages that are powers of two from 8 up). `exact_weights`:
+    the float softmax weights enter the value product as two bfloat16 terms, hi + lo (16 bits of mantissa), for
+    models whose softmax weights are to stay 32-bit; twice the MMAs of that product."""
     _dev(q, k_cache, v_cache, out, query_start, context_lens, block_tables)
     _attn_common(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim)
-    call("tie_attention_prompt_tma", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+    call("tie_attention_prompt_tma_exact" if exact_weights else "tie_attention_prompt_tma", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
          query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], n_seqs,
          max_queries, q_heads, kv_heads, head_dim, k_cache.shape[2], k_cache.shape[0], int(window), float(scale), _stream())
 
@@ -360,9 +362,9 @@ CLUSTER_SPLITS = (2, 4, 8, 16)      # how many splits the decode attention merge
 
 def attention_decode_tma(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim,
                          scale: float, seq_list, n_list: int, split_keys: int, max_splits: int, scratch, counters,
-                         window: int = 0, cluster: bool = False) -> None:
+                         window: int = 0, cluster: bool = False, exact_weights: bool = False) -> None:
     """Attention of sequences that bring one token each, keys and values fed by TMA, splits merged by
-    the last CTA to finish. `counters` (int32 [>= n_list * kv_heads]) must be zero; it is left zero.
+    the last CTA to finish. `exact_weights` as in `attention_prompt_tma`. `counters` (int32 [>= n_list * kv_heads]) must be zero; it is left zero.
     `cluster` (with max_splits in CLUSTER_SPLITS): the splits of a sequence and kv head run as one thread-block
     cluster and merge through shared memory, which is faster where all the launch's CTAs are resident at once.
     `seq_list`: int32 [n_list], or an int: the first of n_list sequences in a row (the kernel then has one load
@@ -378,7 +380,8 @@ def attention_decode_tma(q, k_cache, v_cache, out, query_start, context_lens, bl
           scratch.numel() >= attention_split_scratch_floats(n_list, q_heads, head_dim, max_splits),
           "attention: scratch too small")
     _need(counters.dtype == torch.int32 and counters.numel() >= n_list * kv_heads, "attention: counters too small")
-    call("tie_attention_decode_tma", q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+    call("tie_attention_decode_tma_exact" if exact_weights else "tie_attention_decode_tma", q.data_ptr(), q.stride(0),
+         k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
          query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], q_heads, kv_heads,
          head_dim, k_cache.shape[2], k_cache.shape[0], int(window), float(scale), _ptr(seq_list), first, n_list, split_keys,
          max_splits, scratch.data_ptr(), counters.data_ptr(), 1 if cluster else 0, _stream())
@@ -654,11 +657,13 @@ def attention_split_dv(q, k_cache, v_cache, out, query_start, context_lens, bloc
 
 def delta_prep(proj, q_off: int, k_off: int, v_off: int, b_off: int, conv_w, state, conv_state_off: int, seq_of_row,
                query_start, state_slots, heads: int, kv_heads: int, dim: int, vdim: int, taps: int, unit_eps: float,
-               q_scale: float, qn, kn, vn, beta) -> None:
+               q_scale: float, qn, kn, vn, beta, decay, dt_bias, a_log) -> None:
     """Short causal convolution + SiLU of the q, k, v columns of `proj`, unit norm of q and k per head (q times
     q_scale), sigmoid of the beta columns. `state` [slots, floats] holds, from conv_state_off on, each sequence's
-    last taps - 1 convolution inputs. Outputs are float32: qn, kn [T, kv_heads * dim], vn [T, heads * vdim], beta [T, heads]."""
-    _dev(proj, conv_w, state, seq_of_row, query_start, state_slots, qn, kn, vn, beta)
+    last taps - 1 convolution inputs. Outputs are float32: qn, kn [T, kv_heads * dim], vn [T, heads * vdim], beta [T, heads].
+    `decay` float32 [T, >= heads * dim] (rows may be strided) comes in as the raw decay projection a and leaves as
+    exp(-exp(a_log[h]) softplus(a + dt_bias)) per head and key channel."""
+    _dev(proj, conv_w, state, seq_of_row, query_start, state_slots, qn, kn, vn, beta, decay, dt_bias, a_log)
     T = proj.shape[0]
     nqk, nv = kv_heads * dim, heads * vdim
     _need(proj.dim() == 2 and proj.stride(1) == 1 and max(q_off + nqk, k_off + nqk, v_off + nv, b_off + heads) <= proj.shape[1],
@@ -671,33 +676,34 @@ def delta_prep(proj, q_off: int, k_off: int, v_off: int, b_off: int, conv_w, sta
         _need(t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, n), "delta_prep: outputs must be float32 [T, n]")
     for t in (seq_of_row, query_start, state_slots):
         _need(t.dtype == torch.int32, "delta_prep: index tensors must be int32")
+    _need(decay.dtype == torch.float32 and decay.dim() == 2 and decay.stride(1) == 1 and decay.shape[0] == T and
+          decay.shape[1] >= heads * dim, "delta_prep: decay must be float32 [T, >= heads * dim]")
+    _need(dt_bias.dtype == torch.float32 and dt_bias.numel() == heads * dim and a_log.dtype == torch.float32 and
+          a_log.numel() == heads, "delta_prep: dt_bias float32 [heads * dim], a_log float32 [heads]")
     call("tie_delta_prep", dtype_code(proj), proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, b_off, conv_w.data_ptr(),
          state.data_ptr(), state.stride(0), conv_state_off, seq_of_row.data_ptr(), query_start.data_ptr(),
          state_slots.data_ptr(), T, heads, kv_heads, dim, vdim, taps, float(unit_eps), float(q_scale), qn.data_ptr(),
-         kn.data_ptr(), vn.data_ptr(), beta.data_ptr(), _stream())
+         kn.data_ptr(), vn.data_ptr(), beta.data_ptr(), decay.data_ptr(), decay.stride(0), dt_bias.data_ptr(), a_log.data_ptr(),
+         _stream())
 
 
-def delta_rule(qn, kn, vn, beta, a_raw, dt_bias, a_log, state, conv_state_off: int, proj, q_off: int, k_off: int, v_off: int,
+def delta_rule(qn, kn, vn, beta, decay, state, conv_state_off: int, proj, q_off: int, k_off: int, v_off: int,
                query_start, state_slots, seqs: int, heads: int, kv_heads: int, dim: int, vdim: int, taps: int, out) -> None:
     """The recurrence over each sequence's tokens of the step: per head S <- decay S; u = beta (v - S^T k);
-    S <- S + k u^T; o = S^T q, with decay = exp(-exp(a_log[h]) softplus(a_raw + dt_bias)) per key channel.
+    S <- S + k u^T; o = S^T q, with `decay` float32 [T, >= heads * dim] per head and key channel (`delta_prep`).
     S [heads, dim, vdim] sits at the start of the sequence's row of `state` and is updated; so are the convolution's
-    last inputs (from the q, k, v columns of `proj`). `a_raw` float32 [T, >= heads * dim] (rows may be strided);
-    out float32 [T, heads * vdim]."""
-    _dev(qn, kn, vn, beta, a_raw, dt_bias, a_log, state, proj, query_start, state_slots, out)
+    last inputs (from the q, k, v columns of `proj`). out float32 [T, heads * vdim]."""
+    _dev(qn, kn, vn, beta, decay, state, proj, query_start, state_slots, out)
     T = proj.shape[0]
-    _need(a_raw.dtype == torch.float32 and a_raw.dim() == 2 and a_raw.stride(1) == 1 and a_raw.shape[0] == T and
-          a_raw.shape[1] >= heads * dim, "delta_rule: a_raw must be float32 [T, >= heads * dim]")
-    _need(dt_bias.dtype == torch.float32 and dt_bias.numel() == heads * dim and a_log.dtype == torch.float32 and
-          a_log.numel() == heads, "delta_rule: dt_bias float32 [heads * dim], a_log float32 [heads]")
+    _need(decay.dtype == torch.float32 and decay.dim() == 2 and decay.stride(1) == 1 and decay.shape[0] == T and
+          decay.shape[1] >= heads * dim, "delta_rule: decay must be float32 [T, >= heads * dim]")
     _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (T, heads * vdim), "delta_rule: out must be float32 [T, heads * vdim]")
     _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and conv_state_off >= heads * dim * vdim,
           "delta_rule: state rows too short")
     _need(query_start.numel() >= seqs + 1 and state_slots.numel() >= seqs, "delta_rule: index tensors too short")
-    call("tie_delta_rule", dtype_code(proj), qn.data_ptr(), kn.data_ptr(), vn.data_ptr(), beta.data_ptr(), a_raw.data_ptr(),
-         a_raw.stride(0), dt_bias.data_ptr(), a_log.data_ptr(), state.data_ptr(), state.stride(0), conv_state_off,
-         proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, query_start.data_ptr(), state_slots.data_ptr(), seqs, heads,
-         kv_heads, dim, vdim, taps, out.data_ptr(), _stream())
+    call("tie_delta_rule", dtype_code(proj), qn.data_ptr(), kn.data_ptr(), vn.data_ptr(), beta.data_ptr(), decay.data_ptr(),
+         decay.stride(0), state.data_ptr(), state.stride(0), conv_state_off, proj.data_ptr(), proj.stride(0), q_off, k_off, v_off,
+         query_start.data_ptr(), state_slots.data_ptr(), seqs, heads, kv_heads, dim, vdim, taps, out.data_ptr(), _stream())
 
 
 def delta_out(o, gate, weight, eps: float, out, heads: int, vdim: int) -> None:

@@ -34,8 +34,10 @@ _SIGNATURES = {
     "tie_attention_prompt_tc": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "tie_attention_decode_tc": [P, L, P, P, P, P, P, I, I, I, I, I, I, F, P, I, I, I, P, P],
     "tie_attention_decode_tma": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, I, I, I, I, P, P, I, P],
+    "tie_attention_decode_tma_exact": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, I, I, I, I, P, P, I, P],
     "tie_attention_decode_prep": [P, L, P, L, I, L, P, P, F, F, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, I, I, I, I, P, P, I, P],
     "tie_attention_prompt_tma": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
+    "tie_attention_prompt_tma_exact": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
     "tie_attention_prompt_umma": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
     "tie_attention_merge": [I, P, P, P, I, I, I, P, I, I, I, P, P],
     "tie_attention_rows_dv": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
@@ -45,8 +47,8 @@ _SIGNATURES = {
     "tie_sigmoid_gate_mul": [I, P, L, P, L, I, I, P],
     "tie_scale_rows": [P, L, I, I, F, P],
     "tie_qkv_span_prep": [I, P, L, I, I, I, P, P, P, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, I, P, P, P],
-    "tie_delta_prep": [I, P, L, I, I, I, I, P, P, L, L, P, P, P, I, I, I, I, I, I, F, F, P, P, P, P, P],
-    "tie_delta_rule": [I, P, P, P, P, P, L, P, P, P, L, L, P, L, I, I, I, P, P, I, I, I, I, I, I, P, P],
+    "tie_delta_prep": [I, P, L, I, I, I, I, P, P, L, L, P, P, P, I, I, I, I, I, I, F, F, P, P, P, P, P, L, P, P, P],
+    "tie_delta_rule": [I, P, P, P, P, P, L, P, L, L, P, L, I, I, I, P, P, I, I, I, I, I, I, P, P],
     "tie_delta_out": [I, P, P, L, P, F, P, I, I, I, P],
 }
 

@@ -122,9 +122,9 @@ class ChannelGatedDelta(Mixer):
         beta = ctx.ws.rows("delta.beta", T, H, torch.float32)
         ops.delta_prep(proj, self.q_off, self.k_off, self.v_off, self.b_off, self.conv_w, state, self.state_floats,
                        ctx.seq_of_row, ctx.query_start, ctx.state_slots, H, G, dim, vdim, self.taps, self.unit_eps,
-                       self.q_scale, qn, kn, vn, beta)
+                       self.q_scale, qn, kn, vn, beta, a_raw, self.dt_bias, self.a_log)       # a_raw leaves as the decays
         o = ctx.ws.rows("delta.o", T, self.nv, torch.float32)
-        ops.delta_rule(qn, kn, vn, beta, a_raw, self.dt_bias, self.a_log, state, self.state_floats, proj, self.q_off,
+        ops.delta_rule(qn, kn, vn, beta, a_raw, state, self.state_floats, proj, self.q_off,
                        self.k_off, self.v_off, ctx.query_start, ctx.state_slots, ctx.S, H, G, dim, vdim, self.taps, o)
         gated = ctx.ws.rows("delta.gated", T, self.nv, self.dtype)
         ops.delta_out(o, gate, self.norm_w, self.eps, gated, H, vdim)

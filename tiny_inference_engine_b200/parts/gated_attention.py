@@ -21,7 +21,7 @@ import torch
 from .. import ops
 from ..errors import InvalidArgument
 from ..weights.loader import TensorNeed
-from .attention import MAX_SPLITS, SPLIT_KEYS
+from .attention import MAX_SPLITS, NUM_SMS, SPLIT_KEYS, decode_splits
 from .base import CacheNeed, Mixer, build_part, register_part, to_compute
 
 _MIX_MODES = {None: 0, "none": 0, "source": 1, "blend": 2}
@@ -121,6 +121,45 @@ class GatedWindowAttention(Mixer):
                           table, ctx.positions, g.slots, cache.k, cache.v, H, G, Dk, Dv, self.mix_mode, v_first, self.lam)
         attn = ctx.ws.rows("gattn.out", T, self.o_dim, self.dtype)
         q = proj[:, :self.q_dim]
+        if Dk == Dv and ops.attention_decode_tma_takes(q, H, G, Dk, cache.k.shape[2]):
+            self._attend_tensor_cores(q, attn, ctx, g, cache)
+        else:
+            self._attend_cuda_cores(q, attn, ctx, g, cache)
+        if self.output_gate:
+            ops.sigmoid_gate_mul(attn, proj[:, self.g_off:self.g_off + self.o_dim])
+        out = ctx.ws.rows("mixer.out", T, self.hidden, self.dtype)
+        if self._capacity is None:
+            self._capacity = ops.partial_capacity(ctx.ws.max_rows, self.gemm_o.N, self.gemm_o.K)
+        return self.gemm_o(attn, out, lambda m: ctx.ws.flat("mixer.out.partial", m, torch.float32, self._capacity))
+
+
+    def _attend_tensor_cores(self, q, attn, ctx, g, cache):
+        """bfloat16 with keys and values of one size that the TMA-fed kernels take (64, 128, 256): the score and value
+        products run on the tensor cores with float accumulation; the float softmax weights enter the value product
+        as two bfloat16 terms (`exact_weights`), so that they keep 16 bits of mantissa."""
+        H, G, Dh = self.heads, self.kv_heads, self.head_dim
+        if ctx.multi_rows > 0:
+            ops.attention_prompt_tma(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables, ctx.multi_seqs,
+                                     ctx.multi_max_queries, H, G, Dh, self.scale, self.window, exact_weights=True)
+        if ctx.single_count > 0:
+            longest = ctx.single_max_context if self.window <= 0 else min(ctx.single_max_context, self.window)
+            page = cache.k.shape[2]
+            lens = ctx.single_contexts if self.window <= 0 else None
+            key = ("decode_splits", longest, ctx.single_count, G, page, lens is None)
+            splits = ctx.memo.get(key)
+            if splits is None:
+                splits = ctx.memo[key] = decode_splits(longest, ctx.single_count, G, page, lens)
+            split_keys, max_splits = splits
+            scratch = ctx.ws.flat("attn.split", ops.attention_split_scratch_floats(ctx.max_seqs, H, Dh, MAX_SPLITS), torch.float32)
+            counters = ctx.ws.zeros("attn.counters", ctx.max_seqs * G, torch.int32)
+            cluster = max_splits in ops.CLUSTER_SPLITS and ctx.single_count * G * max_splits <= 2 * NUM_SMS
+            ops.attention_decode_tma(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables, H, G, Dh,
+                                     self.scale, ctx.multi_seqs, ctx.single_count, split_keys, max_splits, scratch, counters,
+                                     self.window, cluster=cluster, exact_weights=True)
+
+    def _attend_cuda_cores(self, q, attn, ctx, g, cache):
+        """float32, or heads of other sizes (keys and values may differ): one warp per (row, head), everything float."""
+        H, G, Dk, Dv = self.heads, self.kv_heads, self.head_dim, self.value_dim
         n = ctx.multi_rows
         if n > 0:
             ops.attention_rows_dv(q[:n], cache.k, cache.v, attn[:n], ctx.seq_of_row[:n], ctx.query_start, ctx.context_lens,
@@ -134,12 +173,6 @@ class GatedWindowAttention(Mixer):
             scratch = ctx.ws.flat("gattn.split", ops.attention_split_scratch_floats(ctx.max_seqs, H, Dv, MAX_SPLITS), torch.float32)
             ops.attention_split_dv(q, cache.k, cache.v, attn, ctx.query_start, ctx.context_lens, g.block_tables, H, G, Dk, Dv,
                                    self.scale, ctx.single_seqs, ctx.single_count, split_keys, max_splits, scratch, self.window)
-        if self.output_gate:
-            ops.sigmoid_gate_mul(attn, proj[:, self.g_off:self.g_off + self.o_dim])
-        out = ctx.ws.rows("mixer.out", T, self.hidden, self.dtype)
-        if self._capacity is None:
-            self._capacity = ops.partial_capacity(ctx.ws.max_rows, self.gemm_o.N, self.gemm_o.K)
-        return self.gemm_o(attn, out, lambda m: ctx.ws.flat("mixer.out.partial", m, torch.float32, self._capacity))
 
 
 def _up8(n: int) -> int:
