@@ -15,8 +15,8 @@
 //   delta_rule   one block per (sequence, head, 16 columns): the recurrence over the sequence's tokens of the
 //                step, state read from and written back to the slot in row pieces through shared memory. Eight
 //                lanes share a column, each holding every eighth key channel; a chunk of tokens is staged in shared
-//                memory at a time. The block of head 0, columns 0 also moves the convolution's last inputs into
-//                the slot.
+//                memory at a time. The blocks of a sequence also move the convolution's last inputs into the
+//                slot, a slice of the channels each.
 //   delta_out    one warp per (token, head): o / rms(o) * w * sigmoid(gate).
 //
 // A state slot is one float row: S of every head [heads, dim, vdim], then the convolution's last taps - 1
@@ -108,10 +108,14 @@ constexpr int kDeltaLanes = 8;       // lanes that share a column of S
 constexpr int kDeltaCols = 16;       // columns of a block (128 threads)
 constexpr int kDeltaPad = kDeltaCols + 1;
 
+// The key channel that register r of lane `lane8` (of the eight that share a column) holds: four channels in a row,
+// then the next four 32 channels on, so that a lane reads its k, q and decay entries 16 bytes at a time.
+__device__ __forceinline__ int delta_row(int r, int lane8) { return (r >> 2) * (4 * kDeltaLanes) + lane8 * 4 + (r & 3); }
+
 // One block per (sequence, head, 16 columns of S). A column's key channels are spread over eight lanes (lane i
 // holds channels i, i + 8, ...), so a token costs one pass over the registers with two dot products (against k and
-// against q of the decayed state), three shuffle steps for both, and the update: with d1 = (gS)^T k and
-// d2 = (gS)^T q, u = beta (v - d1) and the read-out of the updated state is o = d2 + (k . q) u.
+// against q of the decayed state, and k . q beside them), three shuffle steps for the three, and the update: with
+// d1 = (gS)^T k and d2 = (gS)^T q, u = beta (v - d1) and the read-out of the updated state is o = d2 + (k . q) u.
 // RMAX: key channels a lane may hold (dim <= 8 * RMAX).
 template <typename T, int RMAX>
 __global__ void __launch_bounds__(kDeltaLanes * kDeltaCols) delta_rule_kernel(
@@ -142,7 +146,7 @@ __global__ void __launch_bounds__(kDeltaLanes * kDeltaCols) delta_rule_kernel(
   float sreg[RMAX];
 #pragma unroll
   for (int r = 0; r < RMAX; ++r) {
-    const int rowi = lane8 + kDeltaLanes * r;
+    const int rowi = delta_row(r, lane8);
     sreg[r] = rowi < dim ? smem[rowi * kDeltaPad + cidx] : 0.0f;
   }
   float* kb = smem;                           // [chunk][dim]   (the staging tile above is done with)
@@ -150,16 +154,35 @@ __global__ void __launch_bounds__(kDeltaLanes * kDeltaCols) delta_rule_kernel(
   float* gb = qb + chunk * dim;               // decays
   float* vb = gb + chunk * dim;               // [chunk][kDeltaCols]
   float* bb = vb + chunk * kDeltaCols;        // [chunk] beta
-  float* kq = bb + chunk;                     // [chunk] k . q
+  const bool vec4 = dim % 4 == 0;
   for (int c0 = 0; c0 < n; c0 += chunk) {
     const int cn = min(chunk, n - c0);
     __syncthreads();
-    for (int i = threadIdx.x; i < cn * dim; i += blockDim.x) {
-      const int tc = i / dim, d = i % dim;
-      const long long t = t0 + c0 + tc;
-      kb[i] = kn[t * nqk + g * dim + d];
-      qb[i] = qn[t * nqk + g * dim + d];
-      gb[i] = decay[t * decay_stride + h * dim + d];
+    // Each thread brings one key channel of the chunk's tokens, eight tokens' loads in flight at a time (the
+    // recurrence below is short next to a chain of single loads).
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+      const float* kp = kn + static_cast<long long>(t0 + c0) * nqk + g * dim + d;
+      const float* qp = qn + static_cast<long long>(t0 + c0) * nqk + g * dim + d;
+      const float* gp = decay + static_cast<long long>(t0 + c0) * decay_stride + h * dim + d;
+      for (int tc0 = 0; tc0 < cn; tc0 += 8) {
+        float a[8], b[8], c[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          if (tc0 + e < cn) {
+            a[e] = kp[static_cast<long long>(tc0 + e) * nqk];
+            b[e] = qp[static_cast<long long>(tc0 + e) * nqk];
+            c[e] = gp[static_cast<long long>(tc0 + e) * decay_stride];
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          if (tc0 + e < cn) {
+            kb[(tc0 + e) * dim + d] = a[e];
+            qb[(tc0 + e) * dim + d] = b[e];
+            gb[(tc0 + e) * dim + d] = c[e];
+          }
+        }
+      }
     }
     for (int i = threadIdx.x; i < cn * kDeltaCols; i += blockDim.x) {
       const int tc = i / kDeltaCols, c = col0 + i % kDeltaCols;
@@ -167,52 +190,68 @@ __global__ void __launch_bounds__(kDeltaLanes * kDeltaCols) delta_rule_kernel(
     }
     for (int i = threadIdx.x; i < cn; i += blockDim.x) bb[i] = beta[(t0 + c0 + i) * static_cast<long long>(sh.heads) + h];
     __syncthreads();
-    for (int tc = warp; tc < cn; tc += (blockDim.x >> 5)) {
-      float d = 0.0f;
-      for (int e = lane; e < dim; e += 32) d = fmaf(kb[tc * dim + e], qb[tc * dim + e], d);
-      d = warp_sum(d);
-      if (lane == 0) kq[tc] = d;
-    }
-    __syncthreads();
     for (int tc = 0; tc < cn; ++tc) {
       const float* kt = kb + tc * dim;
       const float* qt = qb + tc * dim;
       const float* gt = gb + tc * dim;
-      float d1a = 0.0f, d1b = 0.0f, d2a = 0.0f, d2b = 0.0f;
+      float kreg[RMAX];
+      float d1a = 0.0f, d1b = 0.0f, d2a = 0.0f, d2b = 0.0f, d3 = 0.0f;     // d3: k . q over this lane's channels
 #pragma unroll
-      for (int r = 0; r < RMAX; r += 2) {
-        const int ra = lane8 + kDeltaLanes * r, rb = ra + kDeltaLanes;
-        if (ra < dim) {
-          sreg[r] *= gt[ra];
-          d1a = fmaf(kt[ra], sreg[r], d1a);
-          d2a = fmaf(qt[ra], sreg[r], d2a);
+      for (int q4 = 0; q4 < RMAX / 4; ++q4) {
+        const int r0 = delta_row(4 * q4, lane8);
+        float kk[4], qq[4], gg[4];
+        if (vec4) {                              // dim % 4 == 0: the lane's four channels are one 16-byte piece
+          if (r0 < dim) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kt + r0), q4v = *reinterpret_cast<const float4*>(qt + r0),
+                         g4 = *reinterpret_cast<const float4*>(gt + r0);
+            kk[0] = k4.x, kk[1] = k4.y, kk[2] = k4.z, kk[3] = k4.w;
+            qq[0] = q4v.x, qq[1] = q4v.y, qq[2] = q4v.z, qq[3] = q4v.w;
+            gg[0] = g4.x, gg[1] = g4.y, gg[2] = g4.z, gg[3] = g4.w;
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) kk[e] = qq[e] = gg[e] = 0.0f;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const bool in = r0 + e < dim;
+            kk[e] = in ? kt[r0 + e] : 0.0f;
+            qq[e] = in ? qt[r0 + e] : 0.0f;
+            gg[e] = in ? gt[r0 + e] : 0.0f;
+          }
         }
-        if (rb < dim) {
-          sreg[r + 1] *= gt[rb];
-          d1b = fmaf(kt[rb], sreg[r + 1], d1b);
-          d2b = fmaf(qt[rb], sreg[r + 1], d2b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float sv = sreg[4 * q4 + e] * gg[e];
+          sreg[4 * q4 + e] = sv;
+          kreg[4 * q4 + e] = kk[e];
+          if (e & 1) {
+            d1b = fmaf(kk[e], sv, d1b);
+            d2b = fmaf(qq[e], sv, d2b);
+          } else {
+            d1a = fmaf(kk[e], sv, d1a);
+            d2a = fmaf(qq[e], sv, d2a);
+          }
+          d3 = fmaf(kk[e], qq[e], d3);
         }
       }
       float d1 = d1a + d1b, d2 = d2a + d2b;
-      d1 += __shfl_xor_sync(0xffffffffu, d1, 1);
-      d2 += __shfl_xor_sync(0xffffffffu, d2, 1);
-      d1 += __shfl_xor_sync(0xffffffffu, d1, 2);
-      d2 += __shfl_xor_sync(0xffffffffu, d2, 2);
-      d1 += __shfl_xor_sync(0xffffffffu, d1, 4);
-      d2 += __shfl_xor_sync(0xffffffffu, d2, 4);
-      const float u = bb[tc] * (vb[tc * kDeltaCols + cidx] - d1);
-      if (live && lane8 == 0) out[(t0 + c0 + tc) * static_cast<long long>(nv) + h * vdim + col] = fmaf(kq[tc], u, d2);
 #pragma unroll
-      for (int r = 0; r < RMAX; ++r) {
-        const int rowi = lane8 + kDeltaLanes * r;
-        if (rowi < dim) sreg[r] = fmaf(kt[rowi], u, sreg[r]);
+      for (int o = 1; o < kDeltaLanes; o <<= 1) {
+        d1 += __shfl_xor_sync(0xffffffffu, d1, o);
+        d2 += __shfl_xor_sync(0xffffffffu, d2, o);
+        d3 += __shfl_xor_sync(0xffffffffu, d3, o);
       }
+      const float u = bb[tc] * (vb[tc * kDeltaCols + cidx] - d1);
+      if (live && lane8 == 0) out[(t0 + c0 + tc) * static_cast<long long>(nv) + h * vdim + col] = fmaf(d3, u, d2);
+#pragma unroll
+      for (int r = 0; r < RMAX; ++r) sreg[r] = fmaf(kreg[r], u, sreg[r]);
     }
   }
   __syncthreads();
 #pragma unroll
   for (int r = 0; r < RMAX; ++r) {
-    const int rowi = lane8 + kDeltaLanes * r;
+    const int rowi = delta_row(r, lane8);
     if (rowi < dim) smem[rowi * kDeltaPad + cidx] = sreg[r];
   }
   __syncthreads();
@@ -220,12 +259,15 @@ __global__ void __launch_bounds__(kDeltaLanes * kDeltaCols) delta_rule_kernel(
     const int r = i / kDeltaCols, c = i % kDeltaCols;
     if (col0 + c < vdim) S[static_cast<long long>(r) * vdim + col0 + c] = smem[r * kDeltaPad + c];
   }
-  // The convolution's last taps - 1 inputs after this step: from the step's rows where it brought enough,
-  // else what the slot held moves up.
-  if (h == 0 && blockIdx.z == 0 && sh.taps > 1) {
+  // The convolution's last taps - 1 inputs after this step: from the step's rows where it brought enough, else
+  // what the slot held moves up. Every block of the sequence takes a slice of the channels.
+  if (sh.taps > 1) {
     const int C = 2 * nqk + nv, keep = sh.taps - 1;
+    const int blocks = gridDim.y * gridDim.z, mine = blockIdx.y * gridDim.z + blockIdx.z;
+    const int per = (C + blocks - 1) / blocks;
+    const int c_end = min(C, (mine + 1) * per);
     float* tail = state + slot * state_stride + conv_state_off;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    for (int c = mine * per + threadIdx.x; c < c_end; c += blockDim.x) {
       const int pc = c < nqk ? q_off + c : (c < 2 * nqk ? k_off + (c - nqk) : v_off + (c - 2 * nqk));
       for (int i = 0; i < keep; ++i) {
         const int from = n - keep + i;        // offset in the step of the token that lands at place i
@@ -301,7 +343,7 @@ static int launch_delta_rule(const float* qn, const float* kn, const float* vn, 
                              const int* query_start, const int* state_slots, int seqs, const DeltaShape& sh, float* out,
                              cudaStream_t s) {
   const dim3 grid(seqs, sh.heads, ceil_div(sh.vdim, kDeltaCols));
-  const int per_token = 3 * sh.dim + kDeltaCols + 2;
+  const int per_token = 3 * sh.dim + kDeltaCols + 1;
   int chunk = (40 * 1024 / static_cast<int>(sizeof(float))) / per_token;
   chunk = chunk > 32 ? 32 : (chunk < 1 ? 1 : chunk);
   const int stage = sh.dim * kDeltaPad;                         // the state tile on its way in and out
@@ -312,8 +354,7 @@ static int launch_delta_rule(const float* qn, const float* kn, const float* vn, 
   TIE_LAUNCH((delta_rule_kernel<T, R>), grid, kDeltaLanes * kDeltaCols, smem, s, qn, kn, vn, beta, decay, decay_stride, state, \
              state_stride, conv_state_off, p, proj_stride, q_off, k_off, v_off, query_start, state_slots, sh, chunk, out)
   const int r = (sh.dim + kDeltaLanes - 1) / kDeltaLanes;
-  if (r <= 2) TIE_DELTA_CASE(2);
-  else if (r <= 4) TIE_DELTA_CASE(4);
+  if (r <= 4) TIE_DELTA_CASE(4);
   else if (r <= 8) TIE_DELTA_CASE(8);
   else if (r <= 16) TIE_DELTA_CASE(16);
   else TIE_DELTA_CASE(32);

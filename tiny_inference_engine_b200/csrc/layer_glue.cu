@@ -96,6 +96,47 @@ __global__ void sigmoid_gate_mul_kernel(T* __restrict__ y, long long y_stride, c
   st(p, ld(p) / (1.0f + expf(-g)));
 }
 
+// The same two, 16 bytes a thread (rows whose widths and strides are whole 16-byte pieces).
+template <typename T>
+__global__ void glu_clamped_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, long long total_vecs, float limit,
+                                       float slope, float up_shift) {
+  pdl_sync();
+  constexpr int V = Vec16<T>::N;
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total_vecs) return;
+  const int per_row = inter / V;
+  const long long t = i / per_row;
+  const int c = static_cast<int>(i % per_row) * V;
+  Vec16<T> g, u, y;
+  g.load(gu + t * 2 * inter + c);
+  u.load(gu + t * 2 * inter + inter + c);
+#pragma unroll
+  for (int e = 0; e < V; ++e) {
+    const float gv = fminf(g.v[e], limit);
+    const float uv = fminf(fmaxf(u.v[e], -limit), limit);
+    y.v[e] = (gv / (1.0f + expf(-slope * gv))) * (uv + up_shift);
+  }
+  y.store(out + t * inter + c);
+}
+
+template <typename T>
+__global__ void sigmoid_gate_mul_vec_kernel(T* __restrict__ y, long long y_stride, const T* __restrict__ gate,
+                                            long long gate_stride, int width, long long total_vecs) {
+  pdl_sync();
+  constexpr int V = Vec16<T>::N;
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total_vecs) return;
+  const int per_row = width / V;
+  const long long t = i / per_row;
+  const int c = static_cast<int>(i % per_row) * V;
+  Vec16<T> a, g;
+  a.load(y + t * y_stride + c);
+  g.load(gate + t * gate_stride + c);
+#pragma unroll
+  for (int e = 0; e < V; ++e) a.v[e] = a.v[e] / (1.0f + expf(-g.v[e]));
+  a.store(y + t * y_stride + c);
+}
+
 __global__ void scale_rows_kernel(float* __restrict__ x, long long stride, int width, long long total, float c) {
   pdl_sync();
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -144,12 +185,21 @@ TIE_API int tie_glu_clamped(int dtype, const void* gu, void* out, int tokens, in
   TIE_REQUIRE(tokens >= 0 && inter > 0, "glu_clamped: bad sizes tokens=%d inter=%d", tokens, inter);
   const long long total = static_cast<long long>(tokens) * inter;
   if (total == 0) return kOk;
+  const bool aligned = reinterpret_cast<uintptr_t>(gu) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
   if (dtype == TIE_F32) {
-    TIE_LAUNCH((glu_clamped_kernel<float>), ceil_div(total, 256), 256, 0, s, static_cast<const float*>(gu), static_cast<float*>(out),
-               inter, total, limit, slope, up_shift);
+    if (aligned && inter % 4 == 0)
+      TIE_LAUNCH((glu_clamped_vec_kernel<float>), ceil_div(total / 4, 256), 256, 0, s, static_cast<const float*>(gu),
+                 static_cast<float*>(out), inter, total / 4, limit, slope, up_shift);
+    else
+      TIE_LAUNCH((glu_clamped_kernel<float>), ceil_div(total, 256), 256, 0, s, static_cast<const float*>(gu), static_cast<float*>(out),
+                 inter, total, limit, slope, up_shift);
   } else if (dtype == TIE_BF16) {
-    TIE_LAUNCH((glu_clamped_kernel<__nv_bfloat16>), ceil_div(total, 256), 256, 0, s, static_cast<const __nv_bfloat16*>(gu),
-               static_cast<__nv_bfloat16*>(out), inter, total, limit, slope, up_shift);
+    if (aligned && inter % 8 == 0)
+      TIE_LAUNCH((glu_clamped_vec_kernel<__nv_bfloat16>), ceil_div(total / 8, 256), 256, 0, s, static_cast<const __nv_bfloat16*>(gu),
+                 static_cast<__nv_bfloat16*>(out), inter, total / 8, limit, slope, up_shift);
+    else
+      TIE_LAUNCH((glu_clamped_kernel<__nv_bfloat16>), ceil_div(total, 256), 256, 0, s, static_cast<const __nv_bfloat16*>(gu),
+                 static_cast<__nv_bfloat16*>(out), inter, total, limit, slope, up_shift);
   } else {
     set_error("unknown dtype code %d", dtype);
     return kBadArgument;
@@ -162,12 +212,23 @@ TIE_API int tie_sigmoid_gate_mul(int dtype, void* y, long long y_stride, const v
   TIE_REQUIRE(tokens >= 0 && width > 0, "sigmoid_gate_mul: bad sizes tokens=%d width=%d", tokens, width);
   const long long total = static_cast<long long>(tokens) * width;
   if (total == 0) return kOk;
+  const int vec = dtype == TIE_F32 ? 4 : 8;
+  const bool aligned = reinterpret_cast<uintptr_t>(y) % 16 == 0 && reinterpret_cast<uintptr_t>(gate) % 16 == 0 &&
+                       width % vec == 0 && y_stride % vec == 0 && gate_stride % vec == 0;
   if (dtype == TIE_F32) {
-    TIE_LAUNCH((sigmoid_gate_mul_kernel<float>), ceil_div(total, 256), 256, 0, s, static_cast<float*>(y), y_stride,
-               static_cast<const float*>(gate), gate_stride, width, total);
+    if (aligned)
+      TIE_LAUNCH((sigmoid_gate_mul_vec_kernel<float>), ceil_div(total / 4, 256), 256, 0, s, static_cast<float*>(y), y_stride,
+                 static_cast<const float*>(gate), gate_stride, width, total / 4);
+    else
+      TIE_LAUNCH((sigmoid_gate_mul_kernel<float>), ceil_div(total, 256), 256, 0, s, static_cast<float*>(y), y_stride,
+                 static_cast<const float*>(gate), gate_stride, width, total);
   } else if (dtype == TIE_BF16) {
-    TIE_LAUNCH((sigmoid_gate_mul_kernel<__nv_bfloat16>), ceil_div(total, 256), 256, 0, s, static_cast<__nv_bfloat16*>(y), y_stride,
-               static_cast<const __nv_bfloat16*>(gate), gate_stride, width, total);
+    if (aligned)
+      TIE_LAUNCH((sigmoid_gate_mul_vec_kernel<__nv_bfloat16>), ceil_div(total / 8, 256), 256, 0, s, static_cast<__nv_bfloat16*>(y),
+                 y_stride, static_cast<const __nv_bfloat16*>(gate), gate_stride, width, total / 8);
+    else
+      TIE_LAUNCH((sigmoid_gate_mul_kernel<__nv_bfloat16>), ceil_div(total, 256), 256, 0, s, static_cast<__nv_bfloat16*>(y), y_stride,
+                 static_cast<const __nv_bfloat16*>(gate), gate_stride, width, total);
   } else {
     set_error("unknown dtype code %d", dtype);
     return kBadArgument;
