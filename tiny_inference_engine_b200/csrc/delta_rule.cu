@@ -104,21 +104,30 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(const T* __restrict__ p
   for (int d = threadIdx.x, n = 0; d < width && n < 2; d += blockDim.x, ++n) dst[d] = unit < G ? (vals[n] * inv) * q_scale : vals[n] * inv;
 }
 
-constexpr int kDeltaLanes = 8;       // lanes that share a column of S
-constexpr int kDeltaCols = 16;       // columns of a block (128 threads)
+__device__ __forceinline__ void async_copy4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src) : "memory");
+}
+__device__ __forceinline__ void async_copy16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))), "l"(src) : "memory");
+}
+__device__ __forceinline__ void async_copies_done() { asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory"); }
+
+constexpr int kDeltaCols = 16;       // columns of S that a block holds (LANES threads each)
 constexpr int kDeltaPad = kDeltaCols + 1;
 
-// The key channel that register r of lane `lane8` (of the eight that share a column) holds: four channels in a row,
+// The key channel that register r of lane `lane` (of the LANES that share a column) holds: four channels in a row,
 // then the next four 32 channels on, so that a lane reads its k, q and decay entries 16 bytes at a time.
-__device__ __forceinline__ int delta_row(int r, int lane8) { return (r >> 2) * (4 * kDeltaLanes) + lane8 * 4 + (r & 3); }
+template <int LANES>
+__device__ __forceinline__ int delta_row(int r, int lane) { return (r >> 2) * (4 * LANES) + lane * 4 + (r & 3); }
 
-// One block per (sequence, head, 16 columns of S). A column's key channels are spread over eight lanes (lane i
-// holds channels i, i + 8, ...), so a token costs one pass over the registers with two dot products (against k and
+// One block per (sequence, head, 16 columns of S). A column's key channels are spread over LANES lanes of a warp
+// (8, 16 or 32, by the head size: more lanes mean more warps to hide each other's latencies and fewer registers
+// each), so a token costs one pass over the registers with two dot products (against k and
 // against q of the decayed state, and k . q beside them), three shuffle steps for the three, and the update: with
 // d1 = (gS)^T k and d2 = (gS)^T q, u = beta (v - d1) and the read-out of the updated state is o = d2 + (k . q) u.
-// RMAX: key channels a lane may hold (dim <= 8 * RMAX).
-template <typename T, int RMAX>
-__global__ void __launch_bounds__(kDeltaLanes * kDeltaCols) delta_rule_kernel(
+// RMAX: key channels a lane may hold (dim <= LANES * RMAX).
+template <typename T, int RMAX, int LANES>
+__global__ void __launch_bounds__(LANES * kDeltaCols) delta_rule_kernel(
     const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vn, const float* __restrict__ beta,
     const float* __restrict__ decay, long long decay_stride, float* __restrict__ state, long long state_stride,
     long long conv_state_off, const T* __restrict__ proj, long long proj_stride, int q_off, int k_off, int v_off,
@@ -132,7 +141,7 @@ __global__ void __launch_bounds__(kDeltaLanes * kDeltaCols) delta_rule_kernel(
   const int t0 = query_start[s], n = query_start[s + 1] - t0;
   const int dim = sh.dim, vdim = sh.vdim, nqk = sh.kv_heads * dim, nv = sh.heads * vdim;
   const int g = h / (sh.heads / sh.kv_heads);
-  const int lane8 = threadIdx.x % kDeltaLanes, cidx = threadIdx.x / kDeltaLanes, col = col0 + cidx;
+  const int lane8 = threadIdx.x % LANES, cidx = threadIdx.x / LANES, col = col0 + cidx;      // lane8: the lane among those of its column
   const bool live = col < vdim;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float* S = state + slot * state_stride + static_cast<long long>(h) * dim * vdim;
@@ -146,50 +155,61 @@ __global__ void __launch_bounds__(kDeltaLanes * kDeltaCols) delta_rule_kernel(
   float sreg[RMAX];
 #pragma unroll
   for (int r = 0; r < RMAX; ++r) {
-    const int rowi = delta_row(r, lane8);
+    const int rowi = delta_row<LANES>(r, lane8);
     sreg[r] = rowi < dim ? smem[rowi * kDeltaPad + cidx] : 0.0f;
   }
-  float* kb = smem;                           // [chunk][dim]   (the staging tile above is done with)
-  float* qb = kb + chunk * dim;
-  float* gb = qb + chunk * dim;               // decays
-  float* vb = gb + chunk * dim;               // [chunk][kDeltaCols]
-  float* bb = vb + chunk * kDeltaCols;        // [chunk] beta
+  // Chunks of tokens come through two buffers in turn: while one is worked on, asynchronous copies fill the other.
+  // A buffer: k [chunk][dim], q [chunk][dim], decays [chunk][dim], v [chunk][kDeltaCols], beta [chunk].
+  const int buf_floats = (chunk * (3 * dim + kDeltaCols + 1) + 3) & ~3;      // a buffer starts on a 16-byte boundary
   const bool vec4 = dim % 4 == 0;
-  for (int c0 = 0; c0 < n; c0 += chunk) {
+  const bool wide = vec4 && nqk % 4 == 0 && decay_stride % 4 == 0 && ((reinterpret_cast<uintptr_t>(kn) | reinterpret_cast<uintptr_t>(qn) |
+                                                                      reinterpret_cast<uintptr_t>(decay)) & 15) == 0;
+  auto fetch = [&](int c0, float* base) {
     const int cn = min(chunk, n - c0);
-    __syncthreads();
-    // Each thread brings one key channel of the chunk's tokens, eight tokens' loads in flight at a time (the
-    // recurrence below is short next to a chain of single loads).
-    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-      const float* kp = kn + static_cast<long long>(t0 + c0) * nqk + g * dim + d;
-      const float* qp = qn + static_cast<long long>(t0 + c0) * nqk + g * dim + d;
-      const float* gp = decay + static_cast<long long>(t0 + c0) * decay_stride + h * dim + d;
-      for (int tc0 = 0; tc0 < cn; tc0 += 8) {
-        float a[8], b[8], c[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          if (tc0 + e < cn) {
-            a[e] = kp[static_cast<long long>(tc0 + e) * nqk];
-            b[e] = qp[static_cast<long long>(tc0 + e) * nqk];
-            c[e] = gp[static_cast<long long>(tc0 + e) * decay_stride];
-          }
-        }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          if (tc0 + e < cn) {
-            kb[(tc0 + e) * dim + d] = a[e];
-            qb[(tc0 + e) * dim + d] = b[e];
-            gb[(tc0 + e) * dim + d] = c[e];
-          }
-        }
+    float* kb = base;
+    float* qb = kb + chunk * dim;
+    float* gb = qb + chunk * dim;
+    float* vb = gb + chunk * dim;
+    float* bb = vb + chunk * kDeltaCols;
+    if (wide) {
+      const int pieces = dim / 4;
+      for (int i = threadIdx.x; i < cn * pieces; i += blockDim.x) {
+        const int tc = i / pieces, d = (i % pieces) * 4;
+        const long long t = t0 + c0 + tc;
+        async_copy16(kb + tc * dim + d, kn + t * nqk + g * dim + d);
+        async_copy16(qb + tc * dim + d, qn + t * nqk + g * dim + d);
+        async_copy16(gb + tc * dim + d, decay + t * decay_stride + h * dim + d);
+      }
+    } else {
+      for (int i = threadIdx.x; i < cn * dim; i += blockDim.x) {
+        const int tc = i / dim, d = i % dim;
+        const long long t = t0 + c0 + tc;
+        async_copy4(kb + i, kn + t * nqk + g * dim + d);
+        async_copy4(qb + i, qn + t * nqk + g * dim + d);
+        async_copy4(gb + i, decay + t * decay_stride + h * dim + d);
       }
     }
     for (int i = threadIdx.x; i < cn * kDeltaCols; i += blockDim.x) {
       const int tc = i / kDeltaCols, c = col0 + i % kDeltaCols;
-      vb[i] = c < vdim ? vn[(t0 + c0 + tc) * static_cast<long long>(nv) + h * vdim + c] : 0.0f;
+      if (c < vdim) async_copy4(vb + i, vn + (t0 + c0 + tc) * static_cast<long long>(nv) + h * vdim + c);
+      else vb[i] = 0.0f;
     }
-    for (int i = threadIdx.x; i < cn; i += blockDim.x) bb[i] = beta[(t0 + c0 + i) * static_cast<long long>(sh.heads) + h];
-    __syncthreads();
+    for (int i = threadIdx.x; i < cn; i += blockDim.x) async_copy4(bb + i, beta + (t0 + c0 + i) * static_cast<long long>(sh.heads) + h);
+  };
+  __syncthreads();                            // the staging tile above is done with: the buffers lie over it
+  fetch(0, smem);
+  int turn = 0;
+  for (int c0 = 0; c0 < n; c0 += chunk, turn ^= 1) {
+    const int cn = min(chunk, n - c0);
+    float* base = smem + turn * buf_floats;
+    const float* kb = base;
+    const float* qb = kb + chunk * dim;
+    const float* gb = qb + chunk * dim;
+    const float* vb = gb + chunk * dim;
+    const float* bb = vb + chunk * kDeltaCols;
+    async_copies_done();
+    __syncthreads();                          // this chunk is there, and everyone is through with the other buffer
+    if (c0 + chunk < n) fetch(c0 + chunk, smem + (turn ^ 1) * buf_floats);
     for (int tc = 0; tc < cn; ++tc) {
       const float* kt = kb + tc * dim;
       const float* qt = qb + tc * dim;
@@ -198,7 +218,7 @@ __global__ void __launch_bounds__(kDeltaLanes * kDeltaCols) delta_rule_kernel(
       float d1a = 0.0f, d1b = 0.0f, d2a = 0.0f, d2b = 0.0f, d3 = 0.0f;     // d3: k . q over this lane's channels
 #pragma unroll
       for (int q4 = 0; q4 < RMAX / 4; ++q4) {
-        const int r0 = delta_row(4 * q4, lane8);
+        const int r0 = delta_row<LANES>(4 * q4, lane8);
         float kk[4], qq[4], gg[4];
         if (vec4) {                              // dim % 4 == 0: the lane's four channels are one 16-byte piece
           if (r0 < dim) {
@@ -237,7 +257,7 @@ __global__ void __launch_bounds__(kDeltaLanes * kDeltaCols) delta_rule_kernel(
       }
       float d1 = d1a + d1b, d2 = d2a + d2b;
 #pragma unroll
-      for (int o = 1; o < kDeltaLanes; o <<= 1) {
+      for (int o = 1; o < LANES; o <<= 1) {
         d1 += __shfl_xor_sync(0xffffffffu, d1, o);
         d2 += __shfl_xor_sync(0xffffffffu, d2, o);
         d3 += __shfl_xor_sync(0xffffffffu, d3, o);
@@ -251,7 +271,7 @@ __global__ void __launch_bounds__(kDeltaLanes * kDeltaCols) delta_rule_kernel(
   __syncthreads();
 #pragma unroll
   for (int r = 0; r < RMAX; ++r) {
-    const int rowi = delta_row(r, lane8);
+    const int rowi = delta_row<LANES>(r, lane8);
     if (rowi < dim) smem[rowi * kDeltaPad + cidx] = sreg[r];
   }
   __syncthreads();
@@ -344,20 +364,20 @@ static int launch_delta_rule(const float* qn, const float* kn, const float* vn, 
                              cudaStream_t s) {
   const dim3 grid(seqs, sh.heads, ceil_div(sh.vdim, kDeltaCols));
   const int per_token = 3 * sh.dim + kDeltaCols + 1;
-  int chunk = (40 * 1024 / static_cast<int>(sizeof(float))) / per_token;
-  chunk = chunk > 32 ? 32 : (chunk < 1 ? 1 : chunk);
+  int chunk = (44 * 1024 / static_cast<int>(sizeof(float))) / (2 * per_token);      // two buffers
+  chunk = chunk > 16 ? 16 : (chunk < 1 ? 1 : chunk);
   const int stage = sh.dim * kDeltaPad;                         // the state tile on its way in and out
-  const int floats = chunk * per_token > stage ? chunk * per_token : stage;
+  const int buffers = 2 * ((chunk * per_token + 3) & ~3);
+  const int floats = buffers > stage ? buffers : stage;
   const size_t smem = static_cast<size_t>(floats) * sizeof(float);
   const T* p = static_cast<const T*>(proj);
-#define TIE_DELTA_CASE(R)                                                                                                  \
-  TIE_LAUNCH((delta_rule_kernel<T, R>), grid, kDeltaLanes * kDeltaCols, smem, s, qn, kn, vn, beta, decay, decay_stride, state, \
+#define TIE_DELTA_CASE(R, LANES)                                                                                           \
+  TIE_LAUNCH((delta_rule_kernel<T, R, LANES>), grid, LANES * kDeltaCols, smem, s, qn, kn, vn, beta, decay, decay_stride, state, \
              state_stride, conv_state_off, p, proj_stride, q_off, k_off, v_off, query_start, state_slots, sh, chunk, out)
-  const int r = (sh.dim + kDeltaLanes - 1) / kDeltaLanes;
-  if (r <= 4) TIE_DELTA_CASE(4);
-  else if (r <= 8) TIE_DELTA_CASE(8);
-  else if (r <= 16) TIE_DELTA_CASE(16);
-  else TIE_DELTA_CASE(32);
+  if (sh.dim <= 32) TIE_DELTA_CASE(4, 8);
+  else if (sh.dim <= 64) TIE_DELTA_CASE(4, 16);
+  else if (sh.dim <= 128) TIE_DELTA_CASE(4, 32);
+  else TIE_DELTA_CASE(8, 32);
 #undef TIE_DELTA_CASE
   TIE_RETURN_LAUNCH("delta_rule");
 }
