@@ -27,7 +27,11 @@ ONES = plain.make_config([A(heads=1, kv_heads=1, dim=8, vdim=8, window=1, rot_di
 # keys and values of one size that the tensor-core attention kernels take (bfloat16 runs there)
 SQUARE = plain.make_config([A(heads=4, kv_heads=2, dim=64, vdim=64, window=40, rot_dims=32), D(),
                             A(heads=4, kv_heads=2, dim=64, vdim=64, window=300, rot_dims=64, ff=None)], width=64)
-CONFIGS = {"mixed": (MIXED, dict(low_rank=8, gate_rank=5), 16), "odd": (ODD, dict(low_rank=3, gate_rank=16), 8),
+# value heads smaller than key heads of a size the tensor-core kernels take (bfloat16 keeps them padded with zeros)
+PADDED = plain.make_config([A(heads=4, kv_heads=2, dim=64, vdim=24, window=40, rot_dims=32), D(),
+                            A(heads=8, kv_heads=1, dim=128, vdim=64, window=70, rot_dims=64, v_mix=False, ff=None),
+                            A(heads=4, kv_heads=2, dim=64, vdim=24, window=300, rot_dims=64, ff=None)], width=64)
+CONFIGS = {"padded": (PADDED, dict(low_rank=8, gate_rank=8), 16), "mixed": (MIXED, dict(low_rank=8, gate_rank=5), 16), "odd": (ODD, dict(low_rank=3, gate_rank=16), 8),
            "ones": (ONES, dict(low_rank=1, gate_rank=2), 4), "square": (SQUARE, dict(low_rank=8, gate_rank=8), 16)}
 class Want:
     """The plain implementation's logits, and how far the same implementation moves when its activations are
@@ -137,6 +141,9 @@ SINGLE = {
     "delta": plain.make_config([D()]),
     "delta_one_tap_heads_alike": plain.make_config([D(heads=2, kv_heads=2, conv=1)]),
     "feed_forward_clamps": plain.make_config([D(ff=48, limit=0.4)], residual_mult=2.0),
+    "widths_that_are_no_multiples_of_eight": plain.make_config(
+        [A(heads=2, kv_heads=1, dim=12, vdim=10, window=9, rot_dims=6, ff=50), D(heads=2, kv_heads=1, dim=12, vdim=10, conv=3)],
+        vocab=51, width=36),
     "two_norms_and_scales": plain.make_config([A(v_mix=False, limit=9.0)], eps=1e-2, residual_mult=0.25, logit_scale=3.0),
 }
 
@@ -188,7 +195,7 @@ def test_whole_prompts_decoding_and_portions(tmp_path, truth, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mixed", "odd", "square"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "square", "padded"])
 def test_mixed_batches_on_a_small_pool_with_two_state_slots(tmp_path, truth, name, dtype):
     """Requests of unequal lengths, portions of some beside single tokens of others, never more than two alive:
     pages and state slots are given back and used again, and every row equals the request run alone."""
@@ -256,7 +263,7 @@ def _peaked_attention(window, at, dim=16, vdim=24):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("sizes", [(16, 24), (64, 64)])       # the second pair runs on the tensor cores in bfloat16
+@pytest.mark.parametrize("sizes", [(16, 24), (64, 64), (64, 40)])       # the last two run on the tensor cores in bfloat16
 def test_a_key_just_inside_and_just_outside_the_window(tmp_path, dtype, sizes):
     """A key that dominates every score while it is seen: the rows where it is the window's oldest key and the
     rows right after it left differ visibly, in a prompt, in portions cut at the edge, and token by token, with

@@ -8,7 +8,8 @@
 //   v = proj_v + bv;  mode 1: v_first = v;  mode 2: v = (1 - lambda) v + lambda v_first;  into the value plane
 //
 // One block per token; sums, norms, angles and the blend in float. Planes: keys [pages, kv_heads, page, dim],
-// values [pages, kv_heads, page, vdim].
+// values [pages, kv_heads, page, v_plane] with v_plane >= vdim (a model may keep its value heads padded with zeros
+// to the key heads' size, so that kernels made for one head size serve it).
 #include <math.h>
 
 #include "common.cuh"
@@ -32,6 +33,7 @@ struct PrepArgs {
   void* k_cache;
   void* v_cache;             // null: this layer writes no keys and values
   int q_heads, kv_heads, dim, vdim, page_size;
+  int v_plane;               // width of a row of the value plane (>= vdim; what lies beyond vdim is written as zero)
   int mix_mode;              // 0 none, 1 keep v as v_first, 2 blend with v_first
   float* v_first;            // [T, kv_heads * vdim]
   const float* lambda;       // device scalar
@@ -104,16 +106,18 @@ __global__ void __launch_bounds__(256) qkv_span_prep_kernel(PrepArgs a) {
   }
   const float lam = a.mix_mode == 2 ? *a.lambda : 0.0f;
   T* vc = static_cast<T*>(a.v_cache);
-  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
-    float v = ld(row + a.v_off + i);
-    if (a.bv) v += a.bv[i];
-    float* vf = a.v_first + static_cast<long long>(t) * nv + i;
-    if (a.mix_mode == 1) *vf = v;
-    else if (a.mix_mode == 2) v = (1.0f - lam) * v + lam * *vf;
-    if (slot >= 0) {
-      const int g = i / a.vdim, d = i % a.vdim;
-      st(vc + ((page * a.kv_heads + g) * a.page_size + off) * a.vdim + d, v);
+  for (int i = threadIdx.x; i < a.kv_heads * a.v_plane; i += blockDim.x) {
+    const int g = i / a.v_plane, d = i % a.v_plane;
+    float v = 0.0f;
+    if (d < a.vdim) {
+      const int j = g * a.vdim + d;
+      v = ld(row + a.v_off + j);
+      if (a.bv) v += a.bv[j];
+      float* vf = a.v_first + static_cast<long long>(t) * nv + j;
+      if (a.mix_mode == 1) *vf = v;
+      else if (a.mix_mode == 2) v = (1.0f - lam) * v + lam * *vf;
     }
+    if (slot >= 0) st(vc + ((page * a.kv_heads + g) * a.page_size + off) * a.v_plane + d, v);
   }
 }
 
@@ -124,8 +128,9 @@ using namespace tie;
 TIE_API int tie_qkv_span_prep(int dtype, void* proj, long long stride, int q_off, int k_off, int v_off, const float* bq,
                               const float* bk, const float* bv, const float* wq, const float* wk, float eps,
                               const float* inv_freq, int rot, const int* positions, const int* slots, void* k_cache,
-                              void* v_cache, int tokens, int q_heads, int kv_heads, int dim, int vdim, int page_size,
-                              int mix_mode, float* v_first, const float* lambda, cudaStream_t s) {
+                              void* v_cache, int tokens, int q_heads, int kv_heads, int dim, int vdim, int v_plane,
+                              int page_size, int mix_mode, float* v_first, const float* lambda, cudaStream_t s) {
+  TIE_REQUIRE(v_plane >= vdim, "qkv_span_prep: rows of the value plane (%d) are narrower than a value head (%d)", v_plane, vdim);
   TIE_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && page_size > 0,
               "qkv_span_prep: bad sizes tokens=%d heads=%d/%d dim=%d vdim=%d page=%d", tokens, q_heads, kv_heads, dim, vdim,
               page_size);
@@ -136,7 +141,7 @@ TIE_API int tie_qkv_span_prep(int dtype, void* proj, long long stride, int q_off
   if (tokens == 0) return kOk;
   if (inv_freq == nullptr) rot = 0;
   const PrepArgs a{proj, stride, q_off, k_off, v_off, bq, bk, bv, wq, wk, eps, inv_freq, rot, positions, slots, k_cache,
-                   v_cache, q_heads, kv_heads, dim, vdim, page_size, mix_mode, v_first, lambda};
+                   v_cache, q_heads, kv_heads, dim, vdim, page_size, v_plane, mix_mode, v_first, lambda};
   const int widest = q_heads * dim > kv_heads * dim ? q_heads * dim : kv_heads * dim;
   const size_t smem = static_cast<size_t>(rot + widest) * sizeof(float);
   TIE_REQUIRE(smem <= 200 * 1024, "qkv_span_prep: a projection of %d values does not fit shared memory", widest);

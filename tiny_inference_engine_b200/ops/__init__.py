@@ -575,7 +575,7 @@ def _check_kv_planes(k_cache, v_cache, kv_heads, head_dim, v_dim):
           "cache planes must be [pages, kv_heads, page_size, size] contiguous, alike but for the size")
     _need(k_cache.shape[1] == kv_heads and k_cache.shape[3] == head_dim and v_cache.shape[3] == v_dim,
           "cache planes do not match the heads")
-    _need(max(k_cache.numel() // head_dim, v_cache.numel() // v_dim) < 2 ** 31, "cache plane too large for 32-bit row indices")
+    _need(max(k_cache.numel() // head_dim, v_cache.numel() // v_cache.shape[3]) < 2 ** 31, "cache plane too large for 32-bit row indices")
 
 
 def qkv_span_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, bq, bk, bv, wq, wk, eps: float, inv_freq,
@@ -597,7 +597,8 @@ def qkv_span_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, bq, bk
     page = 1
     if write_kv:
         _need(max(k_off + nk, v_off + nv) <= proj.shape[1], "qkv_span_prep: k or v outside the projection")
-        _check_kv_planes(k_cache, v_cache, kv_heads, head_dim, v_dim)
+        _need(v_cache.dim() == 4 and v_cache.shape[3] >= v_dim, "qkv_span_prep: value plane narrower than a value head")
+        _check_kv_planes(k_cache, v_cache, kv_heads, head_dim, v_cache.shape[3])
         _need(k_cache.dtype == proj.dtype, "qkv_span_prep: dtype differs from the cache's")
         _need(slots.dtype == torch.int32 and slots.numel() == T, "qkv_span_prep: slots must be int32 [T]")
         page = k_cache.shape[2]
@@ -609,7 +610,8 @@ def qkv_span_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, bq, bk
     call("tie_qkv_span_prep", dtype_code(proj), proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, _ptr(bq), _ptr(bk), _ptr(bv),
          _ptr(wq), _ptr(wk), float(eps), _ptr(inv_freq), 2 * inv_freq.numel() if inv_freq is not None else 0,
          positions.data_ptr(), _ptr(slots) if write_kv else 0, _ptr(k_cache) if write_kv else 0,
-         _ptr(v_cache) if write_kv else 0, T, q_heads, kv_heads, head_dim, v_dim, page, int(mix_mode) if write_kv else 0,
+         _ptr(v_cache) if write_kv else 0, T, q_heads, kv_heads, head_dim, v_dim, v_cache.shape[3] if write_kv else v_dim, page,
+         int(mix_mode) if write_kv else 0,
          _ptr(v_first), _ptr(mix_weight), _stream())
 
 

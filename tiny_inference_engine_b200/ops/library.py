@@ -46,7 +46,7 @@ _SIGNATURES = {
     "tie_glu_clamped": [I, P, P, I, I, F, F, F, P],
     "tie_sigmoid_gate_mul": [I, P, L, P, L, I, I, P],
     "tie_scale_rows": [P, L, I, I, F, P],
-    "tie_qkv_span_prep": [I, P, L, I, I, I, P, P, P, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, I, P, P, P],
+    "tie_qkv_span_prep": [I, P, L, I, I, I, P, P, P, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, I, I, P, P, P],
     "tie_delta_prep": [I, P, L, I, I, I, I, P, P, L, L, P, P, P, I, I, I, I, I, I, F, F, P, P, P, P, P, L, P, P, P],
     "tie_delta_rule": [I, P, P, P, P, P, L, P, L, L, P, L, I, I, I, P, P, I, I, I, I, I, I, P, P],
     "tie_delta_out": [I, P, P, L, P, F, P, I, I, I, P],

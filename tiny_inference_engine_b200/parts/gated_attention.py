@@ -51,8 +51,15 @@ class GatedWindowAttention(Mixer):
         self.dtype = dtype
         self.position = build_part("position", p["position"], dtype, prefix=self.prefix)
         self.scale *= float(self.position.score_scale())
+        # bfloat16 value heads smaller than the key heads are kept padded with zeros to the key heads' size (in the
+        # cache, in the heads' outputs, in the gate's rows and in the output product's columns) where that size is
+        # one the tensor-core attention kernels take: `out_dim` is the width a head's output has downstream.
+        self.out_dim = self.value_dim
+        if dtype == torch.bfloat16 and self.value_dim < self.head_dim and self.head_dim in (64, 128, 256) and \
+                self.heads // self.kv_heads <= 16:
+            self.out_dim = self.head_dim
         self.q_dim, self.k_dim = self.heads * self.head_dim, self.kv_heads * self.head_dim
-        self.v_dim, self.o_dim = self.kv_heads * self.value_dim, self.heads * self.value_dim
+        self.v_dim, self.o_dim = self.kv_heads * self.value_dim, self.heads * self.out_dim
         # columns of the stacked product, each section starting at a multiple of 8 (16 bytes of bfloat16)
         self.q_off = 0
         self.k_off = _up8(self.q_dim)
@@ -68,7 +75,7 @@ class GatedWindowAttention(Mixer):
     def needs(self):
         D = self.hidden
         n = {self._name("q"): TensorNeed((self.q_dim, D)), self._name("k"): TensorNeed((self.k_dim, D)),
-             self._name("v"): TensorNeed((self.v_dim, D)), self._name("o"): TensorNeed((D, self.o_dim))}
+             self._name("v"): TensorNeed((self.v_dim, D)), self._name("o"): TensorNeed((D, self.heads * self.value_dim))}
         if self.bias:
             n.update({self._name("q.b"): TensorNeed((self.q_dim,), "norm"), self._name("k.b"): TensorNeed((self.k_dim,), "norm"),
                       self._name("v.b"): TensorNeed((self.v_dim,), "norm"), self._name("o.b"): TensorNeed((D,), "norm")})
@@ -76,21 +83,29 @@ class GatedWindowAttention(Mixer):
             n.update({self._name("q.norm"): TensorNeed((self.q_dim,), "norm"),
                       self._name("k.norm"): TensorNeed((self.k_dim,), "norm")})
         if self.output_gate:
-            n[self._name("g")] = TensorNeed((self.o_dim, D))
-        if self.mix_mode:
-            # the source layer's own weight is never read, but a checkpoint carries it
-            n[self._name("vmix")] = TensorNeed((), "norm", optional=self.mix_mode == 1)
+            n[self._name("g")] = TensorNeed((self.heads * self.value_dim, D))
+        # only a blending layer reads the weight; a checkpoint may carry it for the others too (the source layer's
+        # is never used), so there it is accepted and ignored
+        n[self._name("vmix")] = TensorNeed((), "norm", optional=self.mix_mode != 2)
         n.update(self.position.needs())
         return n
 
     def bind(self, get):
         stacked = torch.zeros((self.width, self.hidden), dtype=self.dtype, device=get(self._name("q")).device)
-        for leaf, off, n in (("q", self.q_off, self.q_dim), ("k", self.k_off, self.k_dim), ("v", self.v_off, self.v_dim)) + \
-                ((("g", self.g_off, self.o_dim),) if self.output_gate else ()):
+        for leaf, off, n in (("q", self.q_off, self.q_dim), ("k", self.k_off, self.k_dim), ("v", self.v_off, self.v_dim)):
             stacked[off:off + n] = to_compute(get(self._name(leaf)), self.dtype)
+        H, Dv, Do = self.heads, self.value_dim, self.out_dim
+        if self.output_gate:      # head h's gate rows at h * out_dim (rows of the padding stay zero: they gate zeros)
+            stacked[self.g_off:self.g_off + self.o_dim].view(H, Do, self.hidden)[:, :Dv] = \
+                to_compute(get(self._name("g")), self.dtype).view(H, Dv, self.hidden)
         self.gemm_in = ops.bound_gemm(stacked, split_many=False)
         self.w_in = self.gemm_in.w
-        self.gemm_o = ops.bound_gemm(to_compute(get(self._name("o")), self.dtype).contiguous(), split_many=True)
+        w_o = to_compute(get(self._name("o")), self.dtype)
+        if Do != Dv:              # columns of the padding are zero
+            padded = torch.zeros((self.hidden, H, Do), dtype=self.dtype, device=w_o.device)
+            padded[:, :, :Dv] = w_o.view(self.hidden, H, Dv)
+            w_o = padded.view(self.hidden, H * Do)
+        self.gemm_o = ops.bound_gemm(w_o.contiguous(), split_many=True)
         self.w_o = self.gemm_o.w
         f32 = lambda leaf: get(self._name(leaf)).to(torch.float32).contiguous()
         self.bq, self.bk, self.bv = (f32("q.b"), f32("k.b"), f32("v.b")) if self.bias else (None, None, None)
@@ -102,12 +117,13 @@ class GatedWindowAttention(Mixer):
 
     def cache_need(self):
         return CacheNeed("window" if self.window > 0 else "full", self.kv_heads, self.head_dim, self.window,
-                         value_dim=0 if self.value_dim == self.head_dim else self.value_dim)
+                         value_dim=0 if self.out_dim == self.head_dim else self.value_dim)
 
     # -- one step
     def forward(self, h, ctx, cache, state):
         T = h.shape[0]
         H, G, Dk, Dv = self.heads, self.kv_heads, self.head_dim, self.value_dim
+        Do = self.out_dim               # a head's width in the value plane and downstream (Dv, or Dk with zeros behind Dv)
         g = ctx.groups[cache.group]
         if not cache.writes:
             raise InvalidArgument("this attention computes its own keys and values: it cannot read another entry's cache")
@@ -121,7 +137,7 @@ class GatedWindowAttention(Mixer):
                           table, ctx.positions, g.slots, cache.k, cache.v, H, G, Dk, Dv, self.mix_mode, v_first, self.lam)
         attn = ctx.ws.rows("gattn.out", T, self.o_dim, self.dtype)
         q = proj[:, :self.q_dim]
-        if Dk == Dv and ops.attention_decode_tma_takes(q, H, G, Dk, cache.k.shape[2]):
+        if Dk == Do and ops.attention_decode_tma_takes(q, H, G, Dk, cache.k.shape[2]):
             self._attend_tensor_cores(q, attn, ctx, g, cache)
         else:
             self._attend_cuda_cores(q, attn, ctx, g, cache)
@@ -159,7 +175,7 @@ class GatedWindowAttention(Mixer):
 
     def _attend_cuda_cores(self, q, attn, ctx, g, cache):
         """float32, or heads of other sizes (keys and values may differ): one warp per (row, head), everything float."""
-        H, G, Dk, Dv = self.heads, self.kv_heads, self.head_dim, self.value_dim
+        H, G, Dk, Dv = self.heads, self.kv_heads, self.head_dim, self.out_dim
         n = ctx.multi_rows
         if n > 0:
             ops.attention_rows_dv(q[:n], cache.k, cache.v, attn[:n], ctx.seq_of_row[:n], ctx.query_start, ctx.context_lens,
