@@ -44,16 +44,39 @@ template <typename T>
 __device__ __forceinline__ void norm_rotate(float* buf, const T* src, const float* bias, const float* w, float eps, int n,
                                             int dim, int rot, const float* cs, float* scratch) {
   float ss = 0.0f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    float v = ld(src + i);
-    if (bias) v += bias[i];
-    buf[i] = v;
-    ss += v * v;
+  const bool wide = n % 4 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(bias) % 16 == 0;
+  if (wide) {                                            // four elements a thread at a time
+    for (int k = 4 * threadIdx.x; k < n; k += 4 * blockDim.x) {
+      float v[4];
+      load4(src + k, v);
+      if (bias) {
+        float b[4];
+        load4(bias + k, b);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] += b[i];
+      }
+      store4(buf + k, v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ss += v[i] * v[i];
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float v = ld(src + i);
+      if (bias) v += bias[i];
+      buf[i] = v;
+      ss += v * v;
+    }
   }
   if (w) {
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / static_cast<float>(n) + eps);
-    for (int i = threadIdx.x; i < n; i += blockDim.x) buf[i] = (buf[i] * inv) * w[i];   // each thread its own elements
+    if (wide) {
+      for (int k = 4 * threadIdx.x; k < n; k += 4 * blockDim.x)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) buf[k + i] = (buf[k + i] * inv) * w[k + i];       // each thread its own elements
+    } else {
+      for (int i = threadIdx.x; i < n; i += blockDim.x) buf[i] = (buf[i] * inv) * w[i];
+    }
   }
   __syncthreads();
   if (cs) {
@@ -77,7 +100,7 @@ __global__ void __launch_bounds__(256) qkv_span_prep_kernel(PrepArgs a) {
   const int t = blockIdx.x;
   const int nq = a.q_heads * a.dim, nk = a.kv_heads * a.dim, nv = a.kv_heads * a.vdim;
   float* cs = smem;                       // [rot]
-  float* buf = smem + a.rot;              // [max(nq, nk)]
+  float* buf = smem + ((a.rot + 3) & ~3); // [max(nq, nk)], on a 16-byte boundary
   T* row = static_cast<T*>(a.proj) + static_cast<long long>(t) * a.stride;
   if (a.inv_freq) {
     const float p = static_cast<float>(a.positions[t]);
@@ -90,7 +113,15 @@ __global__ void __launch_bounds__(256) qkv_span_prep_kernel(PrepArgs a) {
   }
   const float* table = a.inv_freq ? cs : nullptr;
   norm_rotate<T>(buf, row + a.q_off, a.bq, a.wq, a.eps, nq, a.dim, a.rot, table, scratch);
-  for (int i = threadIdx.x; i < nq; i += blockDim.x) st(row + a.q_off + i, buf[i]);
+  if (nq % 4 == 0 && reinterpret_cast<uintptr_t>(row + a.q_off) % 16 == 0) {
+    for (int k = 4 * threadIdx.x; k < nq; k += 4 * blockDim.x) {
+      float v[4];
+      load4(buf + k, v);
+      store4(row + a.q_off + k, v);
+    }
+  } else {
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) st(row + a.q_off + i, buf[i]);
+  }
   if (a.v_cache == nullptr) return;
   __syncthreads();
   const int slot = a.slots[t];
@@ -143,7 +174,7 @@ TIE_API int tie_qkv_span_prep(int dtype, void* proj, long long stride, int q_off
   const PrepArgs a{proj, stride, q_off, k_off, v_off, bq, bk, bv, wq, wk, eps, inv_freq, rot, positions, slots, k_cache,
                    v_cache, q_heads, kv_heads, dim, vdim, page_size, v_plane, mix_mode, v_first, lambda};
   const int widest = q_heads * dim > kv_heads * dim ? q_heads * dim : kv_heads * dim;
-  const size_t smem = static_cast<size_t>(rot + widest) * sizeof(float);
+  const size_t smem = static_cast<size_t>(((rot + 3) & ~3) + widest) * sizeof(float);
   TIE_REQUIRE(smem <= 200 * 1024, "qkv_span_prep: a projection of %d values does not fit shared memory", widest);
   if (dtype == TIE_F32) {
     auto kernel = qkv_span_prep_kernel<float>;

@@ -70,6 +70,75 @@ __global__ void __launch_bounds__(1024) add_normed_rmsnorm_kernel(float* __restr
   for (int k = threadIdx.x; k < dim; k += blockDim.x) st(o + k, (row[k] * inv_x) * w[k]);
 }
 
+// The same for rows of whole 16-byte pieces (dim % 4 == 0): every access is four elements wide.
+template <typename T>
+__global__ void __launch_bounds__(1024) add_normed_rmsnorm_vec4_kernel(float* __restrict__ x, const T* __restrict__ delta,
+                                                                      const float* __restrict__ part, long long part_stride,
+                                                                      int splits, const float* __restrict__ bias,
+                                                                      const float* __restrict__ wb, float eps_b, float mult,
+                                                                      const int* __restrict__ rows, const float* __restrict__ w,
+                                                                      float eps, T* __restrict__ out, int dim) {
+  pdl_sync();
+  extern __shared__ float row[];
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const size_t src = static_cast<size_t>(rows ? rows[t] : t) * dim;
+  float* xr = x + src;
+  const T* dr = delta ? delta + src : nullptr;
+  const float* pr = part ? part + src : nullptr;
+  float ss = 0.0f;
+  for (int k = 4 * threadIdx.x; k < dim; k += 4 * blockDim.x) {
+    float y[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (dr) {
+      load4(dr + k, y);
+    } else {                                                // split by split: each element adds in split order
+#pragma unroll 4
+      for (int z = 0; z < splits; ++z) {
+        float p[4];
+        load4(pr + static_cast<long long>(z) * part_stride + k, p);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) y[i] += p[i];
+      }
+    }
+    if (bias) {
+      float b[4];
+      load4(bias + k, b);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) y[i] += b[i];
+    }
+    store4(row + k, y);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ss += y[i] * y[i];
+  }
+  ss = block_sum(ss, scratch);
+  const float inv_y = 1.0f / sqrtf(ss / static_cast<float>(dim) + eps_b);
+  float sx = 0.0f;
+  for (int k = 4 * threadIdx.x; k < dim; k += 4 * blockDim.x) {      // each thread its own elements of `row`
+    float xv[4], y[4], g[4];
+    load4(xr + k, xv);
+    load4(row + k, y);
+    load4(wb + k, g);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      xv[i] = xv[i] + mult * ((y[i] * inv_y) * g[i]);
+      sx += xv[i] * xv[i];
+    }
+    if (rows == nullptr) store4(xr + k, xv);
+    store4(row + k, xv);
+  }
+  sx = block_sum(sx, scratch);
+  const float inv_x = 1.0f / sqrtf(sx / static_cast<float>(dim) + eps);
+  T* o = out + static_cast<size_t>(t) * dim;
+  for (int k = 4 * threadIdx.x; k < dim; k += 4 * blockDim.x) {
+    float v[4], g[4];
+    load4(row + k, v);
+    load4(w + k, g);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = (v[i] * inv_x) * g[i];
+    store4(o + k, v);
+  }
+}
+
 template <typename T>
 __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, long long total, float limit,
                                    float slope, float up_shift) {
@@ -156,6 +225,15 @@ int launch_add_normed_rmsnorm(float* x, const void* delta, const float* part, lo
       set_error("add_normed_rmsnorm: rows of %d floats do not fit shared memory", dim);
       return kBadArgument;
     }
+  }
+  const auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  if (dim % 4 == 0 && part_stride % 4 == 0 && aligned(x) && aligned(delta) && aligned(part) && aligned(bias) && aligned(wb) &&
+      aligned(w) && aligned(out)) {
+    auto vec = add_normed_rmsnorm_vec4_kernel<T>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(vec, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    TIE_LAUNCH(vec, n, dim >= 8192 ? 1024 : (dim >= 2048 ? 512 : (dim >= 1024 ? 256 : 128)), smem, s, x, static_cast<const T*>(delta),
+               part, part_stride, splits, bias, wb, eps_b, mult, rows, w, eps, static_cast<T*>(out), dim);
+    TIE_RETURN_LAUNCH("add_normed_rmsnorm");
   }
   TIE_LAUNCH(kernel, n, dim >= 4096 ? 1024 : (dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128)), smem, s, x, static_cast<const T*>(delta), part, part_stride, splits, bias, wb,
              eps_b, mult, rows, w, eps, static_cast<T*>(out), dim);
