@@ -178,7 +178,7 @@ def serving_mix(args) -> dict:
         "data": "synthetic (random weights N(0,0.02), uniform random token ids, all requests at time 0)"}
 
 
-# -- the Dugazen design beside Qwen3 at equal sizes (`--design dugazen`; a line of its own, not the contract line)
+# -- the Dugazen design beside Qwen3 at equal sizes (`--design dugazen`; a line of its own, beside the default one)
 
 def dugazen_config(width, layers, heads, kv_heads, ff, vocab, window=1024, vdim=128):
     """Attention and delta-rule layers in turn, every layer with a feed-forward, at the sizes of a Qwen3 layer."""
