@@ -394,3 +394,51 @@ def test_trace_replay_of_a_dugazen_model(tmp_path, truth, dtype):
         close(got, Want(np.concatenate([want[4].rows[80:81], want[0].rows[51:], want[2].rows[63:64]]), noise), dtype, "the rest")
     finally:
         rp.close()
+
+
+# ---------------------------------------------------------------------------------------------- sizes drawn at random
+
+def _random_config(seed):
+    """A configuration with every size, count, constant and the order of layers drawn from what the design allows."""
+    r = np.random.default_rng(seed)
+    pick = lambda *xs: xs[int(r.integers(len(xs)))]
+    kv_v, vdim_mix = pick(1, 2, 3), pick(8, 20, 24, 32, 64)          # blending layers agree on their value heads
+    tensor_core = seed % 3 == 0                                       # every third draw: key heads the tensor cores take
+    layers = []
+    for _ in range(int(r.integers(2, 6))):
+        ff = pick(None, 24, 50, 64)
+        if r.random() < 0.55:
+            mix = bool(r.random() < 0.6)
+            kv = kv_v if mix else pick(1, 2, 4)
+            dim = pick(64, 128) if tensor_core else pick(8, 12, 20, 32, 48)
+            vdim = vdim_mix if mix else pick(4, 16, 40, dim)
+            rot = pick(2, 4, dim // 2 // 2 * 2, dim // 2 * 2)
+            layers.append(A(heads=kv * pick(1, 2, 4), kv_heads=kv, dim=dim, vdim=vdim, window=pick(1, 2, 5, 16, 33, 64, 400),
+                            rot_dims=max(2, rot), base=pick(100.0, 10000.0, 1e6), scale=pick(None, 0.2, 0.05), v_mix=mix, ff=ff,
+                            limit=pick(0.5, 2.0, 7.0)))
+        else:
+            kv = pick(1, 2, 3)
+            layers.append(D(heads=kv * pick(1, 2), kv_heads=kv, dim=pick(8, 12, 32, 40, 64, 128), vdim=pick(4, 16, 20, 36, 64),
+                            conv=pick(1, 2, 3, 4, 5), ff=ff, limit=pick(0.5, 2.0, 7.0)))
+    cfg = plain.make_config(layers, vocab=pick(33, 97, 160, 301), width=pick(24, 36, 64, 72, 128), eps=pick(1e-6, 1e-5, 1e-3),
+                            residual_mult=pick(0.3, 0.7, 1.0, 1.6), logit_scale=pick(0.5, 1.0, 2.5))
+    return cfg, dict(low_rank=pick(1, 3, 8, 24), gate_rank=pick(2, 8, 17)), pick(4, 8, 16, 32)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", range(9))
+def test_configurations_drawn_at_random(tmp_path, seed, dtype):
+    cfg, ranks, page = _random_config(seed)
+    w = plain.random_weights(cfg, 100 + seed, **ranks)
+    a, b = tokens_of(cfg, 83, seed), tokens_of(cfg, 31, 50 + seed)
+    want_a, want_b = reference(w, cfg, a), reference(w, cfg, b)
+    hs = Harness(tmp_path, cfg, w, dtype, page=page, pages=-(-256 // page), slots=2)
+    close(hs.whole("w", a), want_a, dtype, f"seed {seed} whole")
+    rows = hs.step([("a", a[:40], range(40))])
+    rows.update(hs.step([("a", a[40:42], [0, 1]), ("b", b[:17], range(17))]))            # a portion of two beside a prompt
+    rows.update(hs.step([("b", b[17:], range(14)), ("a", a[42:43], [0])], end=["b"]))    # a prompt's end beside one token
+    rows.update(hs.step([("a", a[43:70], range(27))]))
+    for i in range(70, 83):
+        rows.update(hs.step([("a", a[i:i + 1], [0])]))
+    close(np.stack([rows[("a", i)] for i in range(83)]), want_a, dtype, f"seed {seed} in portions and decoded")
+    close(np.stack([rows[("b", i)] for i in range(31)]), want_b, dtype, f"seed {seed} the request beside it")
