@@ -4,7 +4,8 @@ Layers are put into groups by what they need of the cache (kv heads, head size, 
 window of them). Each group has its own page pool and its own storage
 `[planes][2 (K, V)][pages][kv_heads][page_size][head_dim]` (where value heads have a size of their
 own: keys `[planes][pages][kv_heads][page_size][head_dim]` and values likewise with `value_dim`,
-one after the other in one buffer), one plane per run entry of the
+one after the other in one buffer; where a value is the first part of its key, `value_dim` -1, there are
+keys only), one plane per run entry of the
 group; within a group a page id addresses the same token slots in every plane, as in the
 reference's single group (src/kv/paged_kv_cache.h:27-30). A request holds one block table
 per group: token j lives in page table[j // page_size] at offset j % page_size
@@ -34,6 +35,7 @@ from ..errors import CapacityError, InvalidArgument
 from .block_pool import BlockPool
 
 FREED = -1
+VALUES_IN_KEYS = -1      # a CacheNeed.value_dim: the group keeps keys only, a value is the first part of its key
 
 
 def blocks_for(tokens: int, page_size: int) -> int:
@@ -80,7 +82,7 @@ class GroupSpec:
     head_dim: int
     window: int
     entries: tuple[int, ...]   # run entries whose planes live in this group
-    value_dim: int = 0         # size of a value head; 0: head_dim
+    value_dim: int = 0         # size of a value head; 0: head_dim; VALUES_IN_KEYS: no value plane
 
 
 class CacheManager:
@@ -102,7 +104,7 @@ class CacheManager:
             if need is None:
                 continue
             value_dim = getattr(need, "value_dim", 0)
-            if need.kv_heads <= 0 or need.head_dim <= 0 or value_dim < 0 or need.kind not in ("full", "window") or \
+            if need.kv_heads <= 0 or need.head_dim <= 0 or value_dim < VALUES_IN_KEYS or need.kind not in ("full", "window") or \
                     (need.kind == "window" and need.window <= 0):
                 raise InvalidArgument(f"bad cache need of run entry {i}: {need}")
             keyed.setdefault((need.kind, need.kv_heads, need.head_dim, need.window if need.kind == "window" else 0,
@@ -111,8 +113,7 @@ class CacheManager:
         self._entry_group = {e: gi for gi, g in enumerate(self.groups) for e in g.entries}
         self._entry_plane = {e: pi for g in self.groups for pi, e in enumerate(g.entries)}
         elem = 4 if dtype is None else _elem_size(dtype)
-        group_bytes = [len(g.entries) * g.kv_heads * page_size * (g.head_dim + (g.value_dim or g.head_dim)) * elem
-                       for g in self.groups]
+        group_bytes = [len(g.entries) * g.kv_heads * page_size * _row_elems(g) * elem for g in self.groups]
         # what a window group can ever use (None: as many pages as the other groups)
         bounded = [None] * len(self.groups)
         if window_requests is not None:
@@ -142,7 +143,10 @@ class CacheManager:
         if device is not None:
             import torch
             for g, n in zip(self.groups, self.group_pages):
-                if g.value_dim:      # keys of every plane, then values of every plane, in one flat buffer
+                if g.value_dim == VALUES_IN_KEYS:
+                    self.storage.append(torch.zeros((len(g.entries), 1, n, g.kv_heads, page_size, g.head_dim),
+                                                    dtype=dtype, device=device))
+                elif g.value_dim:    # keys of every plane, then values of every plane, in one flat buffer
                     rows = len(g.entries) * n * g.kv_heads * page_size
                     self.storage.append(torch.zeros(rows * (g.head_dim + g.value_dim), dtype=dtype, device=device))
                 else:
@@ -295,6 +299,8 @@ class CacheManager:
         gi, pi = self._entry_group[entry], self._entry_plane[entry]
         st = self.storage[gi]
         g = self.groups[gi]
+        if g.value_dim == VALUES_IN_KEYS:
+            return LayerCache(st[pi, 0], st[pi, 0], gi, writes)
         if g.value_dim:
             n, planes = self.group_pages[gi], len(g.entries)
             rows = n * g.kv_heads * self.page_size
@@ -308,6 +314,13 @@ class CacheManager:
         group gives pages back as it goes and bounds nothing)."""
         full = [n for g, n in zip(self.groups, self.group_pages) if g.kind == "full"]
         return min(full) * self.page_size if full else 2 ** 31 - 1
+
+
+def _row_elems(g: GroupSpec) -> int:
+    """Elements a token holds per kv head in one plane of the group."""
+    if g.value_dim == VALUES_IN_KEYS:
+        return g.head_dim
+    return g.head_dim + (g.value_dim or g.head_dim)
 
 
 def _elem_size(dtype) -> int:

@@ -43,9 +43,13 @@ class LayerSpec:
 class RunEntry:
     """One position of the run order. `layer` indexes `ModelSpec.layers`; a layer may be named by
     several entries. `cache_of` names an EARLIER entry whose cache this entry reads instead
-    of writing its own (its mixer then computes no keys and values)."""
+    of writing its own (its mixer then computes no keys and values). `before` names a part of the family
+    `stream_input` that rewrites the residual stream ahead of this entry's layer (a model that runs a span of layers
+    several times may mix its embedding back in ahead of each pass). Entries that name one layer share its weights
+    and nothing else: each has its own cache plane and its own state."""
     layer: int
     cache_of: int | None = None
+    before: PartSpec | None = None
 
 
 @dataclass(frozen=True)

@@ -39,6 +39,8 @@ struct AttnArgs {
   int window;               // 0 = all keys
   float scale;
   int v_dim;                // size of a value head (and of an output head); keys and queries have head_dim
+  int v_ld;                 // elements between value rows; 0: v_dim. With the key plane given as the value plane too
+                            // and v_ld = head_dim, a value is the first v_dim elements of its key (a latent cache).
 };
 
 // One warp: online softmax over keys [lo, hi] of one (query vector, kv head).
@@ -47,8 +49,8 @@ struct AttnArgs {
 template <typename T, int DPL>
 __device__ __forceinline__ void attend_range(const float* __restrict__ qs, const T* __restrict__ kc,
                                              const T* __restrict__ vc, const int* __restrict__ table, int kvh,
-                                             int kv_heads, int head_dim, int v_dim, int page_size, float scale, int lo,
-                                             int hi, float& m, float& l, float (&acc)[DPL]) {
+                                             int kv_heads, int head_dim, int v_dim, int v_ld, int page_size, float scale,
+                                             int lo, int hi, float& m, float& l, float (&acc)[DPL]) {
   constexpr int V = Vec16<T>::N;
   const int lane = threadIdx.x & 31;
   const int d0 = lane * DPL;
@@ -86,7 +88,7 @@ __device__ __forceinline__ void attend_range(const float* __restrict__ qs, const
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const int rj = __shfl_sync(0xffffffffu, row, jj);
       if (d0 < v_dim) {
-        const T* vr = vc + static_cast<long long>(rj) * v_dim + d0;
+        const T* vr = vc + static_cast<long long>(rj) * v_ld + d0;
 #pragma unroll
         for (int e = 0; e < DPL; ++e)
           if (d0 + e < v_dim) acc[e] = fmaf(pj, ld(vr + e), acc[e]);
@@ -118,7 +120,7 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(AttnArgs a) {
   float m = -INFINITY, l = 0.0f, acc[DPL] = {};
   attend_range<T, DPL>(qs, static_cast<const T*>(a.k_cache), static_cast<const T*>(a.v_cache),
                        a.block_tables + static_cast<long long>(s) * a.max_blocks, kvh, a.kv_heads, a.head_dim,
-                       a.v_dim, a.page_size, a.scale, lo, pos, m, l, acc);
+                       a.v_dim, a.v_ld ? a.v_ld : a.v_dim, a.page_size, a.scale, lo, pos, m, l, acc);
   const int d0 = lane * DPL;
   if (d0 < a.v_dim) {
     T* o = static_cast<T*>(a.out) + (static_cast<long long>(t) * a.q_heads + h) * a.v_dim + d0;
@@ -161,7 +163,7 @@ __global__ void __launch_bounds__(128) attention_split_kernel(AttnArgs a, const 
   float m = -INFINITY, l = 0.0f, acc[DPL] = {};
   attend_range<T, DPL>(qs, static_cast<const T*>(a.k_cache), static_cast<const T*>(a.v_cache),
                        a.block_tables + static_cast<long long>(s) * a.max_blocks, kvh, a.kv_heads, a.head_dim,
-                       a.v_dim, a.page_size, a.scale, lo, hi, m, l, acc);
+                       a.v_dim, a.v_ld ? a.v_ld : a.v_dim, a.page_size, a.scale, lo, hi, m, l, acc);
   float* dst = scratch + ((static_cast<long long>(li) * a.q_heads + h) * max_splits + split) * (a.v_dim + 2);
   const int d0 = lane * DPL;
   if (d0 < a.v_dim) {
@@ -343,9 +345,11 @@ TIE_API int tie_attention_merge(int dtype, void* out, const int* query_start, co
 TIE_API int tie_attention_rows_dv(int dtype, const void* q, long long q_stride, const void* k_cache, const void* v_cache,
                                   void* out, const int* seq_of_row, const int* query_start, const int* context_lens,
                                   const int* block_tables, int max_blocks, int rows, int seqs, int q_heads, int kv_heads,
-                                  int head_dim, int v_dim, int page_size, int window, float scale, cudaStream_t s) {
+                                  int head_dim, int v_dim, int page_size, int window, float scale, int v_ld,
+                                  cudaStream_t s) {
   const AttnArgs a{q, k_cache, v_cache, out, seq_of_row, query_start, context_lens, block_tables, q_stride, max_blocks,
-                   rows, seqs, q_heads, kv_heads, head_dim, page_size, window, scale, v_dim};
+                   rows, seqs, q_heads, kv_heads, head_dim, page_size, window, scale, v_dim, v_ld};
+  TIE_REQUIRE(v_ld == 0 || v_ld >= v_dim, "attention: value rows %d apart are shorter than a value head of %d", v_ld, v_dim);
   if (const int st = check_attn(a, true)) return st;
   if (dtype == TIE_F32) return launch_attention<float>(a, nullptr, nullptr, 0, 0, 0, nullptr, 1, s);
   if (dtype == TIE_BF16) return launch_attention<__nv_bfloat16>(a, nullptr, nullptr, 0, 0, 0, nullptr, 1, s);
@@ -357,9 +361,10 @@ TIE_API int tie_attention_split_dv(int dtype, const void* q, long long q_stride,
                                    void* out, const int* query_start, const int* context_lens, const int* block_tables,
                                    int max_blocks, int seqs, int q_heads, int kv_heads, int head_dim, int v_dim,
                                    int page_size, int window, float scale, const int* seq_list, int n_list, int split_keys,
-                                   int max_splits, float* scratch, cudaStream_t s) {
+                                   int max_splits, float* scratch, int v_ld, cudaStream_t s) {
   const AttnArgs a{q, k_cache, v_cache, out, nullptr, query_start, context_lens, block_tables, q_stride, max_blocks,
-                   0, seqs, q_heads, kv_heads, head_dim, page_size, window, scale, v_dim};
+                   0, seqs, q_heads, kv_heads, head_dim, page_size, window, scale, v_dim, v_ld};
+  TIE_REQUIRE(v_ld == 0 || v_ld >= v_dim, "attention: value rows %d apart are shorter than a value head of %d", v_ld, v_dim);
   if (const int st = check_attn(a, true)) return st;
   TIE_REQUIRE(split_keys > 0 && max_splits > 0 && max_splits <= kMergeMaxSplits && scratch != nullptr,
               "attention split: bad split geometry (at most %d splits)", kMergeMaxSplits);

@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(LANES * kDeltaCols) delta_rule_kernel(
     const float* __restrict__ decay, long long decay_stride, float* __restrict__ state, long long state_stride,
     long long conv_state_off, const T* __restrict__ proj, long long proj_stride, int q_off, int k_off, int v_off,
     const int* __restrict__ query_start, const int* __restrict__ state_slots, DeltaShape sh, int chunk,
-    float* __restrict__ out) {
+    float* __restrict__ out, int plain, int decay_per_head) {
   pdl_sync();
   extern __shared__ float smem[];
   const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kDeltaCols;
@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(LANES * kDeltaCols) delta_rule_kernel(
   // A buffer: k [chunk][dim], q [chunk][dim], decays [chunk][dim], v [chunk][kDeltaCols], beta [chunk].
   const int buf_floats = (chunk * (3 * dim + kDeltaCols + 1) + 3) & ~3;      // a buffer starts on a 16-byte boundary
   const bool vec4 = dim % 4 == 0;
-  const bool wide = vec4 && nqk % 4 == 0 && decay_stride % 4 == 0 && ((reinterpret_cast<uintptr_t>(kn) | reinterpret_cast<uintptr_t>(qn) |
+  const bool wide = !decay_per_head && vec4 && nqk % 4 == 0 && decay_stride % 4 == 0 && ((reinterpret_cast<uintptr_t>(kn) | reinterpret_cast<uintptr_t>(qn) |
                                                                       reinterpret_cast<uintptr_t>(decay)) & 15) == 0;
   auto fetch = [&](int c0, float* base) {
     const int cn = min(chunk, n - c0);
@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(LANES * kDeltaCols) delta_rule_kernel(
         const long long t = t0 + c0 + tc;
         async_copy4(kb + i, kn + t * nqk + g * dim + d);
         async_copy4(qb + i, qn + t * nqk + g * dim + d);
-        async_copy4(gb + i, decay + t * decay_stride + h * dim + d);
+        async_copy4(gb + i, decay + t * decay_stride + (decay_per_head ? h : h * dim + d));
       }
     }
     for (int i = threadIdx.x; i < cn * kDeltaCols; i += blockDim.x) {
@@ -194,7 +194,10 @@ __global__ void __launch_bounds__(LANES * kDeltaCols) delta_rule_kernel(
       if (c < vdim) async_copy4(vb + i, vn + (t0 + c0 + tc) * static_cast<long long>(nv) + h * vdim + c);
       else vb[i] = 0.0f;
     }
-    for (int i = threadIdx.x; i < cn; i += blockDim.x) async_copy4(bb + i, beta + (t0 + c0 + i) * static_cast<long long>(sh.heads) + h);
+    for (int i = threadIdx.x; i < cn; i += blockDim.x) {
+      if (beta) async_copy4(bb + i, beta + (t0 + c0 + i) * static_cast<long long>(sh.heads) + h);
+      else bb[i] = 1.0f;
+    }
   };
   __syncthreads();                            // the staging tile above is done with: the buffers lie over it
   fetch(0, smem);
@@ -262,7 +265,7 @@ __global__ void __launch_bounds__(LANES * kDeltaCols) delta_rule_kernel(
         d2 += __shfl_xor_sync(0xffffffffu, d2, o);
         d3 += __shfl_xor_sync(0xffffffffu, d3, o);
       }
-      const float u = bb[tc] * (vb[tc * kDeltaCols + cidx] - d1);
+      const float u = plain ? bb[tc] * vb[tc * kDeltaCols + cidx] : bb[tc] * (vb[tc * kDeltaCols + cidx] - d1);
       if (live && lane8 == 0) out[(t0 + c0 + tc) * static_cast<long long>(nv) + h * vdim + col] = fmaf(d3, u, d2);
 #pragma unroll
       for (int r = 0; r < RMAX; ++r) sreg[r] = fmaf(kreg[r], u, sreg[r]);
@@ -361,7 +364,7 @@ static int launch_delta_rule(const float* qn, const float* kn, const float* vn, 
                              long long decay_stride, float* state, long long state_stride, long long conv_state_off,
                              const void* proj, long long proj_stride, int q_off, int k_off, int v_off,
                              const int* query_start, const int* state_slots, int seqs, const DeltaShape& sh, float* out,
-                             cudaStream_t s) {
+                             int plain, int decay_per_head, cudaStream_t s) {
   const dim3 grid(seqs, sh.heads, ceil_div(sh.vdim, kDeltaCols));
   const int per_token = 3 * sh.dim + kDeltaCols + 1;
   int chunk = (44 * 1024 / static_cast<int>(sizeof(float))) / (2 * per_token);      // two buffers
@@ -373,7 +376,8 @@ static int launch_delta_rule(const float* qn, const float* kn, const float* vn, 
   const T* p = static_cast<const T*>(proj);
 #define TIE_DELTA_CASE(R, LANES)                                                                                           \
   TIE_LAUNCH((delta_rule_kernel<T, R, LANES>), grid, LANES * kDeltaCols, smem, s, qn, kn, vn, beta, decay, decay_stride, state, \
-             state_stride, conv_state_off, p, proj_stride, q_off, k_off, v_off, query_start, state_slots, sh, chunk, out)
+             state_stride, conv_state_off, p, proj_stride, q_off, k_off, v_off, query_start, state_slots, sh, chunk, out, plain, \
+             decay_per_head)
   if (sh.dim <= 32) TIE_DELTA_CASE(4, 8);
   else if (sh.dim <= 64) TIE_DELTA_CASE(4, 16);
   else if (sh.dim <= 128) TIE_DELTA_CASE(4, 32);
@@ -386,17 +390,18 @@ TIE_API int tie_delta_rule(int dtype, const float* qn, const float* kn, const fl
                            const float* decay, long long decay_stride, float* state, long long state_stride,
                            long long conv_state_off, const void* proj, long long proj_stride, int q_off, int k_off,
                            int v_off, const int* query_start, const int* state_slots, int seqs, int heads, int kv_heads,
-                           int dim, int vdim, int taps, float* out, cudaStream_t s) {
+                           int dim, int vdim, int taps, float* out, int plain, int decay_per_head, cudaStream_t s) {
   const DeltaShape sh{heads, kv_heads, dim, vdim, taps};
   if (const int st_ = check_delta(sh)) return st_;
   if (seqs <= 0) return kOk;
+  TIE_REQUIRE(beta != nullptr || plain, "delta_rule: the delta rule needs beta");
   TIE_REQUIRE(seqs <= 65535 * 32 && heads <= 65535, "delta_rule: %d sequences x %d heads exceed the grid", seqs, heads);
   if (dtype == TIE_F32)
     return launch_delta_rule<float>(qn, kn, vn, beta, decay, decay_stride, state, state_stride, conv_state_off, proj, proj_stride,
-                                    q_off, k_off, v_off, query_start, state_slots, seqs, sh, out, s);
+                                    q_off, k_off, v_off, query_start, state_slots, seqs, sh, out, plain, decay_per_head, s);
   if (dtype == TIE_BF16)
     return launch_delta_rule<__nv_bfloat16>(qn, kn, vn, beta, decay, decay_stride, state, state_stride, conv_state_off, proj,
-                                            proj_stride, q_off, k_off, v_off, query_start, state_slots, seqs, sh, out, s);
+                                            proj_stride, q_off, k_off, v_off, query_start, state_slots, seqs, sh, out, plain, decay_per_head, s);
   set_error("unknown dtype code %d", dtype);
   return kBadArgument;
 }

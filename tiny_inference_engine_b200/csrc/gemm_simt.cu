@@ -17,8 +17,10 @@ namespace tie {
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256) gemm_tiled_kernel(const TI* __restrict__ a, const TI* __restrict__ w,
                                                          TO* __restrict__ out, int M, int N, int K, long long lda,
-                                                         long long ldw, long long ldo) {
+                                                         long long ldw, long long ldo, long long sa, long long sw,
+                                                         long long so) {
   pdl_sync();
+  a += blockIdx.z * sa, w += blockIdx.z * sw, out += blockIdx.z * so;      // one product of a batch (strides 0: the only one)
   constexpr int BM = 64, BN = 64, BK = 16;
   __shared__ float as[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
@@ -71,8 +73,10 @@ __global__ void __launch_bounds__(256) gemm_tiled_kernel(const TI* __restrict__ 
 template <typename TI, typename TO, int MT>
 __global__ void __launch_bounds__(256) gemm_small_m_kernel(const TI* __restrict__ a, const TI* __restrict__ w,
                                                            TO* __restrict__ out, int M, int N, int K, long long lda,
-                                                           long long ldw, long long ldo) {
+                                                           long long ldw, long long ldo, long long sa, long long sw,
+                                                           long long so) {
   pdl_sync();
+  a += blockIdx.z * sa, w += blockIdx.z * sw, out += blockIdx.z * so;
   constexpr int V = Vec16<TI>::N;
   const int lane = threadIdx.x & 31;
   const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -102,24 +106,26 @@ __global__ void __launch_bounds__(256) gemm_small_m_kernel(const TI* __restrict_
 
 template <typename TI, typename TO>
 int launch_gemm(const void* a, const void* w, void* out, int M, int N, int K, long long lda, long long ldw,
-                long long ldo, cudaStream_t s) {
-  if (M == 0 || N == 0) return kOk;
+                long long ldo, cudaStream_t s, int batch = 1, long long sa = 0, long long sw = 0, long long so = 0) {
+  if (M == 0 || N == 0 || batch == 0) return kOk;
   const TI* ap = static_cast<const TI*>(a);
   const TI* wp = static_cast<const TI*>(w);
   TO* op = static_cast<TO*>(out);
   constexpr int V = Vec16<TI>::N;
-  const bool vec_ok = K % V == 0 && lda % V == 0 && ldw % V == 0 &&
+  const bool vec_ok = K % V == 0 && lda % V == 0 && ldw % V == 0 && sa % V == 0 && sw % V == 0 &&
                       reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0;
   if (M <= 16 && vec_ok) {
     const dim3 block(256);
     if (M <= 4) {
-      TIE_LAUNCH((gemm_small_m_kernel<TI, TO, 4>), dim3(ceil_div(N, 8), 1), block, 0, s, ap, wp, op, M, N, K, lda, ldw, ldo);
+      TIE_LAUNCH((gemm_small_m_kernel<TI, TO, 4>), dim3(ceil_div(N, 8), 1, batch), block, 0, s, ap, wp, op, M, N, K, lda, ldw, ldo,
+                 sa, sw, so);
     } else {
-      TIE_LAUNCH((gemm_small_m_kernel<TI, TO, 8>), dim3(ceil_div(N, 8), ceil_div(M, 8)), block, 0, s, ap, wp, op, M, N, K, lda,
-                                                                                            ldw, ldo);
+      TIE_LAUNCH((gemm_small_m_kernel<TI, TO, 8>), dim3(ceil_div(N, 8), ceil_div(M, 8), batch), block, 0, s, ap, wp, op, M, N, K,
+                 lda, ldw, ldo, sa, sw, so);
     }
   } else {
-    TIE_LAUNCH((gemm_tiled_kernel<TI, TO>), dim3(ceil_div(N, 64), ceil_div(M, 64)), 256, 0, s, ap, wp, op, M, N, K, lda, ldw, ldo);
+    TIE_LAUNCH((gemm_tiled_kernel<TI, TO>), dim3(ceil_div(N, 64), ceil_div(M, 64), batch), 256, 0, s, ap, wp, op, M, N, K, lda, ldw,
+               ldo, sa, sw, so);
   }
   TIE_RETURN_LAUNCH("gemm_simt");
 }
@@ -139,6 +145,23 @@ TIE_API int tie_gemm_simt(int in_dtype, int out_dtype, const void* a, const void
     return launch_gemm<__nv_bfloat16, __nv_bfloat16>(a, w, out, M, N, K, lda, ldw, ldo, s);
   if (in_dtype == TIE_BF16 && out_dtype == TIE_F32)
     return launch_gemm<__nv_bfloat16, float>(a, w, out, M, N, K, lda, ldw, ldo, s);
+  set_error("gemm: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
+  return kBadArgument;
+}
+
+// `batch` products at once: product b reads a + b * sa and w + b * sw and writes out + b * so (strides in elements).
+// With sa = K and so = N inside rows lda and ldo apart, the batch is the heads of a row: out[t, b, :] = w[b] a[t, b, :].
+TIE_API int tie_gemm_simt_batched(int in_dtype, int out_dtype, const void* a, const void* w, void* out, int M, int N, int K,
+                                  long long lda, long long ldw, long long ldo, int batch, long long sa, long long sw,
+                                  long long so, cudaStream_t s) {
+  TIE_REQUIRE(M >= 0 && N >= 0 && K > 0 && batch >= 0 && batch <= 65535, "gemm: bad sizes M=%d N=%d K=%d batch=%d", M, N, K, batch);
+  TIE_REQUIRE(ldw >= K, "gemm: a row stride is smaller than the row");
+  if (in_dtype == TIE_F32 && out_dtype == TIE_F32)
+    return launch_gemm<float, float>(a, w, out, M, N, K, lda, ldw, ldo, s, batch, sa, sw, so);
+  if (in_dtype == TIE_BF16 && out_dtype == TIE_BF16)
+    return launch_gemm<__nv_bfloat16, __nv_bfloat16>(a, w, out, M, N, K, lda, ldw, ldo, s, batch, sa, sw, so);
+  if (in_dtype == TIE_BF16 && out_dtype == TIE_F32)
+    return launch_gemm<__nv_bfloat16, float>(a, w, out, M, N, K, lda, ldw, ldo, s, batch, sa, sw, so);
   set_error("gemm: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
   return kBadArgument;
 }

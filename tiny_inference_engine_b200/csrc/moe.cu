@@ -1,0 +1,274 @@
+// A feed-forward made of many small experts of which each token uses a few.
+//
+//   moe_route   one warp per token: softmax over all experts' logits (float), the best `keep` of `groups` equal
+//               blocks of consecutive experts by their best member, then the `top` best experts of those groups
+//               (ties go to the lower index); weights are the chosen scores over their sum (+ 1e-20).
+//   moe_align   one block: counts the (token, choice) pairs of every expert, gives each expert a range of rows
+//               that is a whole number of tiles of `block_m` rows, and lists the pairs in that order (-1 pads a
+//               tile). Also says which expert each tile belongs to and how many tiles there are, all on the
+//               device: nothing of a step's routing is read by the host, so a step can be a captured graph.
+//   moe_gemm    grouped products on the CUDA cores, one block per (tile of rows, 64 output columns): rows are
+//               gathered through the list, weights are the tile's expert's. `first` reads token rows and writes a
+//               row per pair; `second` reads a row per pair and writes weight * result as the pair's choice-th
+//               partial sum of the token, float [top, tokens, N]: whoever adds the feed-forward's output to the
+//               residual stream adds those `top` terms in order, in float.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace tie {
+
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) v = ov, i = oi;
+  }
+}
+
+// smem per warp: experts floats (scores), experts floats (work), groups floats, groups ints.
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, long long ld_logits, int tokens,
+                                                        int experts, int top, int groups, int keep, int* __restrict__ ids,
+                                                        float* __restrict__ weights) {
+  pdl_sync();
+  extern __shared__ float smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long t = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp;
+  if (t >= tokens) return;
+  float* score = smem + warp * (2 * experts + 2 * groups);
+  float* work = score + experts;
+  float* gbest = work + experts;
+  int* gsel = reinterpret_cast<int*>(gbest + groups);
+  const float* z = logits + t * ld_logits;
+  float m = -INFINITY;
+  for (int e = lane; e < experts; e += 32) m = fmaxf(m, z[e]);
+  m = warp_max(m);
+  float sum = 0.0f;
+  for (int e = lane; e < experts; e += 32) {
+    const float p = expf(z[e] - m);
+    score[e] = p;
+    sum += p;
+  }
+  sum = warp_sum(sum);
+  const float inv = 1.0f / sum;
+  for (int e = lane; e < experts; e += 32) {
+    const float s = score[e] * inv;
+    score[e] = s;
+    work[e] = s;
+  }
+  __syncwarp();
+  const int per = experts / groups;
+  if (keep < groups) {
+    for (int g = lane; g < groups; g += 32) {
+      float b = -1.0f;
+      for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, score[e]);
+      gbest[g] = b;
+      gsel[g] = 0;
+    }
+    __syncwarp();
+    for (int k = 0; k < keep; ++k) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32)
+        if (gbest[g] > bv) bv = gbest[g], bi = g;
+      warp_argmax(bv, bi);
+      if (bi >= groups) bi = k;            // nothing comparable (a row of NaN): any group
+      if (lane == 0) gsel[bi] = 1, gbest[bi] = -2.0f;
+      __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32)
+      if (!gsel[e / per]) work[e] = -1.0f;
+    __syncwarp();
+  }
+  float total = 0.0f;
+  float mine_w = 0.0f;
+  int mine_e = 0;
+  for (int k = 0; k < top; ++k) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32)
+      if (work[e] > bv) bv = work[e], bi = e;
+    warp_argmax(bv, bi);
+    if (bi >= experts) bi = k % experts;
+    const float s = score[bi];
+    total += s;
+    if (lane == (k & 31)) mine_w = s, mine_e = bi;     // top <= 32 is checked by the launcher
+    __syncwarp();
+    if (lane == 0) work[bi] = -1.0f;
+    __syncwarp();
+  }
+  if (lane < top) {
+    ids[t * top + lane] = mine_e;
+    weights[t * top + lane] = mine_w / (total + 1e-20f);
+  }
+}
+
+// meta[0] = number of tiles. smem: 2 * experts ints.
+__global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__ ids, int pairs, int experts, int block_m,
+                                                         int* __restrict__ sorted, int* __restrict__ tile_expert,
+                                                         int* __restrict__ meta) {
+  pdl_sync();
+  extern __shared__ int ismem[];
+  int* count = ismem;
+  int* cursor = ismem + experts;
+  __shared__ int total_rows;
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&count[ids[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int row = 0;
+    for (int e = 0; e < experts; ++e) {
+      cursor[e] = row;
+      const int tiles = (count[e] + block_m - 1) / block_m;
+      for (int i = 0; i < tiles; ++i) tile_expert[row / block_m + i] = e;
+      row += tiles * block_m;
+    }
+    total_rows = row;
+    meta[0] = row / block_m;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < total_rows; i += blockDim.x) sorted[i] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) sorted[atomicAdd(&cursor[ids[i]], 1)] = i;
+}
+
+// out rows for a tile of BM gathered rows against the 64 weight rows [n0, n0 + 64) of the tile's expert.
+// SECOND false: a row = token pair / top of `a`; out[pair] in TO. SECOND true: a row = pair of `a`; the result times
+// weights[pair] goes to partial[(pair % top)][pair / top] (float).
+template <typename TI, typename TO, int BM, bool SECOND>
+__global__ void __launch_bounds__(256) moe_gemm_kernel(const TI* __restrict__ a, long long lda, const TI* __restrict__ w,
+                                                       long long w_expert_stride, TO* __restrict__ out, long long ldo,
+                                                       float* __restrict__ partial, long long part_stride,
+                                                       const float* __restrict__ weights, const int* __restrict__ sorted,
+                                                       const int* __restrict__ tile_expert, const int* __restrict__ meta,
+                                                       int top, int N, int K) {
+  pdl_sync();
+  constexpr int BN = 64, BK = 16, RM = BM / 16;
+  const int tile = blockIdx.y;
+  if (tile >= meta[0]) return;
+  __shared__ float as[BK][BM + 4];
+  __shared__ float ws[BK][BN + 4];
+  __shared__ int pair_of[BM];
+  const int tid = threadIdx.x;
+  if (tid < BM) pair_of[tid] = sorted[tile * BM + tid];
+  __syncthreads();
+  const TI* we = w + static_cast<long long>(tile_expert[tile]) * w_expert_stride;
+  const int n0 = blockIdx.x * BN;
+  const int tm = (tid / 16) * RM, tn = (tid % 16) * 4;
+  // loads: the weight tile is 64 x 16 (four k a thread); the row tile BM x 16
+  const int wr = tid / 4, wk = (tid % 4) * 4;
+  constexpr int A_PER = BM * BK / 256;                 // 4 (BM 64) or 1 (BM 16)
+  const int ar = BM == 64 ? tid / 4 : tid / 16, ak = BM == 64 ? (tid % 4) * 4 : tid % 16;
+  const int pa = pair_of[ar];
+  const TI* arow = pa < 0 ? nullptr : a + static_cast<long long>(SECOND ? pa : pa / top) * lda;
+  float acc[RM][4] = {};
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int k = k0 + wk + j, n = n0 + wr;
+      ws[wk + j][wr] = (n < N && k < K) ? ld(we + static_cast<long long>(n) * K + k) : 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < A_PER; ++j) {
+      const int k = k0 + ak + j;
+      as[ak + j][ar] = (arow != nullptr && k < K) ? ld(arow + k) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      float av[RM], wv[4];
+#pragma unroll
+      for (int i = 0; i < RM; ++i) av[i] = as[k][tm + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) wv[j] = ws[k][tn + j];
+#pragma unroll
+      for (int i = 0; i < RM; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < RM; ++i) {
+    const int pair = pair_of[tm + i];
+    if (pair < 0) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tn + j;
+      if (n >= N) continue;
+      if (SECOND) partial[(pair % top) * part_stride + static_cast<long long>(pair / top) * N + n] = weights[pair] * acc[i][j];
+      else st(out + static_cast<long long>(pair) * ldo + n, acc[i][j]);
+    }
+  }
+}
+
+}  // namespace tie
+
+using namespace tie;
+
+TIE_API int tie_moe_route(const float* logits, long long ld_logits, int tokens, int experts, int top, int groups, int keep,
+                          int* ids, float* weights, cudaStream_t s) {
+  TIE_REQUIRE(experts > 0 && top > 0 && top <= 32 && top <= experts && groups > 0 && experts % groups == 0 && keep > 0 &&
+                  keep <= groups && top <= keep * (experts / groups),
+              "moe_route: bad routing experts=%d top=%d (at most 32) groups=%d keep=%d", experts, top, groups, keep);
+  if (tokens <= 0) return kOk;
+  const size_t smem = 4 * sizeof(float) * (2 * experts + 2 * groups);
+  TIE_REQUIRE(smem <= 48 * 1024, "moe_route: %d experts exceed the kernel's shared memory", experts);
+  TIE_LAUNCH(moe_route_kernel, ceil_div(tokens, 4), 128, smem, s, logits, ld_logits, tokens, experts, top, groups, keep, ids, weights);
+  TIE_RETURN_LAUNCH("moe_route");
+}
+
+TIE_API int tie_moe_align(const int* ids, int pairs, int experts, int block_m, int* sorted, int* tile_expert, int* meta,
+                          cudaStream_t s) {
+  TIE_REQUIRE(experts > 0 && experts <= 4096 && (block_m == 16 || block_m == 64), "moe_align: bad sizes experts=%d block_m=%d", experts, block_m);
+  if (pairs <= 0) return kOk;
+  TIE_LAUNCH(moe_align_kernel, 1, 1024, 2 * experts * sizeof(int), s, ids, pairs, experts, block_m, sorted, tile_expert, meta);
+  TIE_RETURN_LAUNCH("moe_align");
+}
+
+// The most tiles `pairs` pairs over `experts` experts can need.
+TIE_API int tie_moe_max_tiles(int pairs, int experts, int block_m) {
+  const int full = pairs / block_m;
+  return full + (experts < pairs ? experts : pairs);
+}
+
+template <typename TI, typename TO>
+static int launch_moe_gemm(int second, int block_m, const void* a, long long lda, const void* w, long long w_expert_stride,
+                           void* out, long long ldo, float* partial, long long part_stride, const float* weights,
+                           const int* sorted, const int* tile_expert, const int* meta, int max_tiles, int top, int N, int K,
+                           cudaStream_t s) {
+  const dim3 grid(ceil_div(N, 64), max_tiles);
+#define TIE_MOE_CASE(BM, SECOND)                                                                                            \
+  TIE_LAUNCH((moe_gemm_kernel<TI, TO, BM, SECOND>), grid, 256, 0, s, static_cast<const TI*>(a), lda, static_cast<const TI*>(w), \
+             w_expert_stride, static_cast<TO*>(out), ldo, partial, part_stride, weights, sorted, tile_expert, meta, top, N, K)
+  if (block_m == 64) {
+    if (second) TIE_MOE_CASE(64, true);
+    else TIE_MOE_CASE(64, false);
+  } else {
+    if (second) TIE_MOE_CASE(16, true);
+    else TIE_MOE_CASE(16, false);
+  }
+#undef TIE_MOE_CASE
+  TIE_RETURN_LAUNCH("moe_gemm");
+}
+
+// second 0: out[pair, :N] = w[expert] a[pair / top]; second 1: partial[pair % top][pair / top][:N] = weights[pair] * (w[expert] a[pair]).
+// w is [experts, N, K] (an expert's rows K apart, experts w_expert_stride apart).
+TIE_API int tie_moe_gemm(int dtype, int second, int block_m, const void* a, long long lda, const void* w,
+                         long long w_expert_stride, void* out, long long ldo, float* partial, long long part_stride,
+                         const float* weights, const int* sorted, const int* tile_expert, const int* meta, int max_tiles,
+                         int top, int N, int K, cudaStream_t s) {
+  TIE_REQUIRE(N > 0 && K > 0 && top > 0 && (block_m == 16 || block_m == 64) && max_tiles >= 0 && max_tiles <= 65535,
+              "moe_gemm: bad sizes N=%d K=%d top=%d block_m=%d tiles=%d", N, K, top, block_m, max_tiles);
+  if (max_tiles == 0) return kOk;
+  if (dtype == TIE_F32)
+    return launch_moe_gemm<float, float>(second, block_m, a, lda, w, w_expert_stride, out, ldo, partial, part_stride, weights, sorted,
+                                         tile_expert, meta, max_tiles, top, N, K, s);
+  if (dtype == TIE_BF16)
+    return launch_moe_gemm<__nv_bfloat16, __nv_bfloat16>(second, block_m, a, lda, w, w_expert_stride, out, ldo, partial, part_stride,
+                                                         weights, sorted, tile_expert, meta, max_tiles, top, N, K, s);
+  set_error("unknown dtype code %d", dtype);
+  return kBadArgument;
+}

@@ -615,8 +615,14 @@ def qkv_span_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, bq, bk
          _ptr(v_first), _ptr(mix_weight), _stream())
 
 
-def _attn_common_dv(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim, v_dim):
-    _check_kv_planes(k_cache, v_cache, kv_heads, head_dim, v_dim)
+def _attn_common_dv(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim, v_dim,
+                    values_in_keys: bool = False):
+    if values_in_keys:
+        _need(v_cache is k_cache or v_cache.data_ptr() == k_cache.data_ptr(), "attention: values in keys take the key plane twice")
+        _need(v_dim <= head_dim, "attention: a value inside its key cannot be longer than the key")
+        _check_kv_planes(k_cache, k_cache, kv_heads, head_dim, head_dim)
+    else:
+        _check_kv_planes(k_cache, v_cache, kv_heads, head_dim, v_dim)
     _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= q_heads * head_dim, "attention: q too narrow")
     _need(out.shape == (q.shape[0], q_heads * v_dim) and out.is_contiguous(), "attention: out must be [T, Hq*Dv]")
     _need(q.dtype == k_cache.dtype and out.dtype == q.dtype, "attention: q, cache and out must have one dtype")
@@ -629,30 +635,34 @@ def _attn_common_dv(q, k_cache, v_cache, out, query_start, context_lens, block_t
 
 
 def attention_rows_dv(q, k_cache, v_cache, out, seq_of_row, query_start, context_lens, block_tables, q_heads, kv_heads,
-                      head_dim, v_dim, scale: float, window: int = 0) -> None:
-    """`attention_rows` for keys of head_dim and values of v_dim (out [T, q_heads * v_dim])."""
+                      head_dim, v_dim, scale: float, window: int = 0, values_in_keys: bool = False) -> None:
+    """`attention_rows` for keys of head_dim and values of v_dim (out [T, q_heads * v_dim]). `values_in_keys`: there
+    is no value plane; a value is the first v_dim elements of its key (pass the key plane as `v_cache`)."""
     _dev(q, k_cache, v_cache, out, seq_of_row, query_start, context_lens, block_tables)
-    S = _attn_common_dv(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim, v_dim)
+    S = _attn_common_dv(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim, v_dim,
+                        values_in_keys)
     _need(seq_of_row.dtype == torch.int32 and seq_of_row.numel() == q.shape[0], "attention: seq_of_row must be int32 [T]")
     call("tie_attention_rows_dv", dtype_code(q), q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
          out.data_ptr(), seq_of_row.data_ptr(), query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(),
          block_tables.shape[1], q.shape[0], S, q_heads, kv_heads, head_dim, v_dim, k_cache.shape[2], int(window), float(scale),
-         _stream())
+         head_dim if values_in_keys else 0, _stream())
 
 
 def attention_split_dv(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim, v_dim,
-                       scale: float, seq_list, n_list: int, split_keys: int, max_splits: int, scratch, window: int = 0) -> None:
+                       scale: float, seq_list, n_list: int, split_keys: int, max_splits: int, scratch, window: int = 0,
+                       values_in_keys: bool = False) -> None:
     """`attention_split` for keys of head_dim and values of v_dim; scratch holds
-    attention_split_scratch_floats(n_list, q_heads, v_dim, max_splits) floats."""
+    attention_split_scratch_floats(n_list, q_heads, v_dim, max_splits) floats. `values_in_keys` as in `attention_rows_dv`."""
     _dev(q, k_cache, v_cache, out, query_start, context_lens, block_tables, seq_list, scratch)
-    S = _attn_common_dv(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim, v_dim)
+    S = _attn_common_dv(q, k_cache, v_cache, out, query_start, context_lens, block_tables, q_heads, kv_heads, head_dim, v_dim,
+                        values_in_keys)
     _need(seq_list.dtype == torch.int32 and seq_list.numel() >= n_list, "attention: seq_list must be int32 [n_list]")
     _need(scratch.dtype == torch.float32 and
           scratch.numel() >= attention_split_scratch_floats(n_list, q_heads, v_dim, max_splits), "attention: scratch too small")
     call("tie_attention_split_dv", dtype_code(q), q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
          out.data_ptr(), query_start.data_ptr(), context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
          S, q_heads, kv_heads, head_dim, v_dim, k_cache.shape[2], int(window), float(scale), seq_list.data_ptr(), n_list,
-         split_keys, max_splits, scratch.data_ptr(), _stream())
+         split_keys, max_splits, scratch.data_ptr(), head_dim if values_in_keys else 0, _stream())
 
 
 # -- the gated delta rule with a decay per key channel (csrc/delta_rule.cu)
@@ -690,22 +700,28 @@ def delta_prep(proj, q_off: int, k_off: int, v_off: int, b_off: int, conv_w, sta
 
 
 def delta_rule(qn, kn, vn, beta, decay, state, conv_state_off: int, proj, q_off: int, k_off: int, v_off: int,
-               query_start, state_slots, seqs: int, heads: int, kv_heads: int, dim: int, vdim: int, taps: int, out) -> None:
+               query_start, state_slots, seqs: int, heads: int, kv_heads: int, dim: int, vdim: int, taps: int, out,
+               plain: bool = False, decay_per_head: bool = False) -> None:
     """The recurrence over each sequence's tokens of the step: per head S <- decay S; u = beta (v - S^T k);
     S <- S + k u^T; o = S^T q, with `decay` float32 [T, >= heads * dim] per head and key channel (`delta_prep`).
     S [heads, dim, vdim] sits at the start of the sequence's row of `state` and is updated; so are the convolution's
-    last inputs (from the q, k, v columns of `proj`). out float32 [T, heads * vdim]."""
+    last inputs (from the q, k, v columns of `proj`). out float32 [T, heads * vdim].
+    `plain`: no correction, u = beta v (beta None: u = v), which is the recurrence of gated linear attention and of
+    state-space layers, S <- diag(decay) S + k u^T. `decay_per_head`: decay is float32 [T, >= heads], one factor for
+    all key channels of a head."""
     _dev(qn, kn, vn, beta, decay, state, proj, query_start, state_slots, out)
     T = proj.shape[0]
+    _need(beta is not None or plain, "delta_rule: the delta rule needs beta")
     _need(decay.dtype == torch.float32 and decay.dim() == 2 and decay.stride(1) == 1 and decay.shape[0] == T and
-          decay.shape[1] >= heads * dim, "delta_rule: decay must be float32 [T, >= heads * dim]")
+          decay.shape[1] >= (heads if decay_per_head else heads * dim), "delta_rule: decay must be float32 [T, >= heads * dim]")
     _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (T, heads * vdim), "delta_rule: out must be float32 [T, heads * vdim]")
     _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and conv_state_off >= heads * dim * vdim,
           "delta_rule: state rows too short")
     _need(query_start.numel() >= seqs + 1 and state_slots.numel() >= seqs, "delta_rule: index tensors too short")
-    call("tie_delta_rule", dtype_code(proj), qn.data_ptr(), kn.data_ptr(), vn.data_ptr(), beta.data_ptr(), decay.data_ptr(),
+    call("tie_delta_rule", dtype_code(proj), qn.data_ptr(), kn.data_ptr(), vn.data_ptr(), _ptr(beta), decay.data_ptr(),
          decay.stride(0), state.data_ptr(), state.stride(0), conv_state_off, proj.data_ptr(), proj.stride(0), q_off, k_off, v_off,
-         query_start.data_ptr(), state_slots.data_ptr(), seqs, heads, kv_heads, dim, vdim, taps, out.data_ptr(), _stream())
+         query_start.data_ptr(), state_slots.data_ptr(), seqs, heads, kv_heads, dim, vdim, taps, out.data_ptr(),
+         1 if plain else 0, 1 if decay_per_head else 0, _stream())
 
 
 def delta_out(o, gate, weight, eps: float, out, heads: int, vdim: int) -> None:
@@ -720,3 +736,236 @@ def delta_out(o, gate, weight, eps: float, out, heads: int, vdim: int) -> None:
     _need(out.is_contiguous() and out.shape == o.shape, "delta_out: out must be [T, heads * vdim] contiguous")
     call("tie_delta_out", dtype_code(out), o.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(), float(eps),
          out.data_ptr(), T, heads, vdim, _stream())
+
+
+# -- what stands around the plain recurrence for gated linear attention and state-space layers (csrc/linear_recurrence.cu)
+
+def gla_prep(proj, q_off: int, k_off: int, v_off: int, heads: int, dim: int, vdim: int, q_scale: float, tau: float, z_bias,
+             qn, kn, vn, decay) -> None:
+    """q (times q_scale), k and v columns of `proj` as float32 rows qn, kn [T, heads * dim], vn [T, heads * vdim];
+    `decay` float32 [T, >= heads * dim] comes in as the raw decay projection z and leaves as
+    sigmoid(z + z_bias)^(1 / tau) per head and key channel."""
+    _dev(proj, z_bias, qn, kn, vn, decay)
+    T = proj.shape[0]
+    nqk, nv = heads * dim, heads * vdim
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and max(q_off + nqk, k_off + nqk, v_off + nv) <= proj.shape[1],
+          "gla_prep: columns outside the projection")
+    for t, n in ((qn, nqk), (kn, nqk), (vn, nv)):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, n), "gla_prep: outputs must be float32 [T, n]")
+    _need(decay.dtype == torch.float32 and decay.dim() == 2 and decay.stride(1) == 1 and decay.shape[0] == T and
+          decay.shape[1] >= nqk, "gla_prep: decay must be float32 [T, >= heads * dim]")
+    _need(z_bias is None or (z_bias.dtype == torch.float32 and z_bias.numel() == nqk), "gla_prep: the bias must be float32 [heads * dim]")
+    call("tie_gla_prep", dtype_code(proj), proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, T, heads, dim, vdim,
+         float(q_scale), float(tau), _ptr(z_bias), qn.data_ptr(), kn.data_ptr(), vn.data_ptr(), decay.data_ptr(),
+         decay.stride(0), _stream())
+
+
+def ssd_prep(proj, c_off: int, b_off: int, x_off: int, dt_off: int, conv_w, conv_b, state, conv_state_off: int, seq_of_row,
+             query_start, state_slots, heads: int, groups: int, state_size: int, vdim: int, taps: int, dt_bias, a_log,
+             cn, bn, xn, dt, decay) -> None:
+    """Short causal convolution (+ bias) and SiLU of the C, B and x columns of `proj` (conv_w float32 [channels, taps],
+    channels in the order C, B, x; the last tap weighs the current token) to float32 cn, bn [T, groups * state_size] and
+    xn [T, heads * vdim]; dt = softplus(proj[dt_off + h] + dt_bias[h]) and decay = exp(-exp(a_log[h]) dt), float32 [T, heads].
+    `state` [slots, floats] holds, from conv_state_off on, each sequence's last taps - 1 convolution inputs."""
+    _dev(proj, conv_w, conv_b, state, seq_of_row, query_start, state_slots, dt_bias, a_log, cn, bn, xn, dt, decay)
+    T = proj.shape[0]
+    ngn, nv = groups * state_size, heads * vdim
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and max(c_off + ngn, b_off + ngn, x_off + nv, dt_off + heads) <= proj.shape[1],
+          "ssd_prep: columns outside the projection")
+    _need(conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape == (2 * ngn + nv, taps),
+          "ssd_prep: convolution weights must be float32 [channels, taps]")
+    _need(conv_b is None or (conv_b.dtype == torch.float32 and conv_b.numel() == 2 * ngn + nv), "ssd_prep: convolution bias must be float32 [channels]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and
+          conv_state_off + (taps - 1) * (2 * ngn + nv) <= state.shape[1], "ssd_prep: state rows too short")
+    for t, n in ((cn, ngn), (bn, ngn), (xn, nv), (dt, heads), (decay, heads)):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, n), "ssd_prep: outputs must be float32 [T, n]")
+    for t in (seq_of_row, query_start, state_slots):
+        _need(t.dtype == torch.int32, "ssd_prep: index tensors must be int32")
+    for t in (dt_bias, a_log):
+        _need(t.dtype == torch.float32 and t.numel() == heads, "ssd_prep: dt_bias and a_log must be float32 [heads]")
+    call("tie_ssd_prep", dtype_code(proj), proj.data_ptr(), proj.stride(0), c_off, b_off, x_off, dt_off, conv_w.data_ptr(),
+         _ptr(conv_b), state.data_ptr(), state.stride(0), conv_state_off, seq_of_row.data_ptr(), query_start.data_ptr(),
+         state_slots.data_ptr(), T, heads, groups, state_size, vdim, taps, dt_bias.data_ptr(), a_log.data_ptr(),
+         cn.data_ptr(), bn.data_ptr(), xn.data_ptr(), dt.data_ptr(), decay.data_ptr(), _stream())
+
+
+GATE_SIGMOID, GATE_SILU = 0, 1
+
+
+def head_norm_gate(o, gate, weight, eps: float, out, heads: int, vdim: int, act: int = GATE_SIGMOID) -> None:
+    """out[t, h] = (o[t, h] / rms(o[t, h])) * weight * act(gate[t, h]) per head of vdim; o float32, gate (rows may be
+    strided) and out in the compute dtype; act GATE_SIGMOID or GATE_SILU."""
+    _dev(o, gate, weight, out)
+    T = o.shape[0]
+    _need(o.dtype == torch.float32 and o.is_contiguous() and o.shape == (T, heads * vdim), "head_norm_gate: o must be float32 [T, heads * vdim]")
+    _need(gate.dim() == 2 and gate.stride(1) == 1 and gate.shape == o.shape and gate.dtype == out.dtype,
+          "head_norm_gate: gate must be [T, heads * vdim] in out's dtype")
+    _need(weight.dtype == torch.float32 and weight.numel() == vdim, "head_norm_gate: weight must be float32 [vdim]")
+    _need(out.is_contiguous() and out.shape == o.shape, "head_norm_gate: out must be [T, heads * vdim] contiguous")
+    call("tie_head_norm_gate", dtype_code(out), o.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(), float(eps),
+         out.data_ptr(), T, heads, vdim, int(act), _stream())
+
+
+def ssd_out(o, xn, z, skip, weight, eps: float, out, heads: int, vdim: int, parts: int) -> None:
+    """out = norm_parts((o + skip[h] xn) * silu(z)) * weight: the gate comes before the norm, and each of `parts` equal
+    parts of the row is divided by its own root mean square. o, xn float32 [T, heads * vdim]; z (rows may be strided)
+    and out in the compute dtype; skip float32 [heads]; weight float32 [heads * vdim]."""
+    _dev(o, xn, z, skip, weight, out)
+    T, inner = o.shape[0], heads * vdim
+    for t in (o, xn):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, inner), "ssd_out: o and xn must be float32 [T, heads * vdim]")
+    _need(z.dim() == 2 and z.stride(1) == 1 and z.shape == (T, inner) and z.dtype == out.dtype, "ssd_out: z must be [T, heads * vdim] in out's dtype")
+    _need(skip.dtype == torch.float32 and skip.numel() == heads and weight.dtype == torch.float32 and weight.numel() == inner,
+          "ssd_out: skip float32 [heads], weight float32 [heads * vdim]")
+    _need(out.is_contiguous() and out.shape == (T, inner), "ssd_out: out must be [T, heads * vdim] contiguous")
+    call("tie_ssd_out", dtype_code(out), o.data_ptr(), xn.data_ptr(), z.data_ptr(), z.stride(0), skip.data_ptr(),
+         weight.data_ptr(), float(eps), out.data_ptr(), T, heads, vdim, int(parts), _stream())
+
+
+# -- attention over one latent per token (csrc/attention_latent.cu) and products batched over heads
+
+def latent_prep(proj, q_off: int, q_rank: int, kv_off: int, rank: int, rot: int, wq, wkv, eps: float, inv_freq, positions,
+                slots, cq, k_cache) -> None:
+    """From the stacked down-projections of every token: cq [T, q_rank] = rmsnorm(proj[q_off:]) * wq; the key plane's row
+    at the token's slot = [rmsnorm(proj[kv_off : kv_off + rank]) * wkv | rotation of the `rot` columns behind them]."""
+    _dev(proj, wq, wkv, inv_freq, positions, slots, cq, k_cache)
+    T = proj.shape[0]
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and max(q_off + q_rank, kv_off + rank + rot) <= proj.shape[1],
+          "latent_prep: columns outside the projection")
+    _need(wq.dtype == torch.float32 and wq.numel() == q_rank and wkv.dtype == torch.float32 and wkv.numel() == rank,
+          "latent_prep: norm weights must be float32 of the latents' sizes")
+    _need(rot == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and 2 * inv_freq.numel() == rot),
+          "latent_prep: inv_freq must be float32 [rot / 2]")
+    _need(positions.dtype == torch.int32 and positions.numel() == T and slots.dtype == torch.int32 and slots.numel() == T,
+          "latent_prep: positions and slots must be int32 [T]")
+    _need(cq.shape == (T, q_rank) and cq.is_contiguous() and cq.dtype == proj.dtype, "latent_prep: cq must be [T, q_rank] contiguous")
+    _need(k_cache.dim() == 4 and k_cache.is_contiguous() and k_cache.shape[1] == 1 and k_cache.shape[3] == rank + rot and
+          k_cache.dtype == proj.dtype, "latent_prep: the key plane must be [pages, 1, page_size, rank + rot]")
+    call("tie_latent_prep", dtype_code(proj), proj.data_ptr(), proj.stride(0), q_off, q_rank, kv_off, rank, rot, wq.data_ptr(),
+         wkv.data_ptr(), float(eps), _ptr(inv_freq), positions.data_ptr(), slots.data_ptr(), cq.data_ptr(), k_cache.data_ptr(),
+         T, _stream())
+
+
+def latent_query_rot(q, dim: int, rot: int, inv_freq, positions, folded, rank: int, heads: int) -> None:
+    """folded[t, h, rank : rank + rot] = rotation of q[t, h, dim : dim + rot] (heads of dim + rot in q, of rank + rot in folded)."""
+    _dev(q, inv_freq, positions, folded)
+    T = q.shape[0]
+    _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= heads * (dim + rot) and folded.dim() == 2 and folded.stride(1) == 1
+          and folded.shape == (T, heads * (rank + rot)) and folded.dtype == q.dtype, "latent_query_rot: q [T, heads * (dim + rot)], folded [T, heads * (rank + rot)]")
+    _need(rot == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and 2 * inv_freq.numel() == rot),
+          "latent_query_rot: inv_freq must be float32 [rot / 2]")
+    _need(positions.dtype == torch.int32 and positions.numel() == T, "latent_query_rot: positions must be int32 [T]")
+    call("tie_latent_query_rot", dtype_code(q), q.data_ptr(), q.stride(0), dim, rot, _ptr(inv_freq), positions.data_ptr(),
+         folded.data_ptr(), folded.stride(0), rank, heads, T, _stream())
+
+
+def head_gate_mul(y, gate, heads: int, head_size: int) -> None:
+    """y[t, h, :] *= sigmoid(gate[t, h]) in place: one gate per head. y [T, heads * head_size], gate [T, heads] (rows may be strided)."""
+    _dev(y, gate)
+    T = y.shape[0]
+    _need(y.dim() == 2 and y.stride(1) == 1 and y.shape[1] == heads * head_size and gate.dim() == 2 and gate.stride(1) == 1 and
+          gate.shape == (T, heads) and gate.dtype == y.dtype, "head_gate_mul: y [T, heads * head_size] and gate [T, heads] of one dtype")
+    call("tie_head_gate_mul", dtype_code(y), y.data_ptr(), y.stride(0), gate.data_ptr(), gate.stride(0), T, heads, head_size, _stream())
+
+
+def gemm_heads(a, w, out, heads: int) -> None:
+    """out[t, h, :] = w[h] a[t, h, :] for every head: a [T, >= heads * K] with head h at column h * a_head (a_head =
+    a.shape[1] // heads), w [heads, N, K] contiguous, out [T, heads * out_head] with the result in the first N
+    columns of each head. Float accumulation on the CUDA cores; a and w of one dtype."""
+    _dev(a, w, out)
+    T = a.shape[0]
+    _need(a.dim() == 2 and out.dim() == 2 and w.dim() == 3 and w.is_contiguous() and w.shape[0] == heads, "gemm_heads: a, out 2-D, w [heads, N, K]")
+    _need(a.stride(1) == 1 and out.stride(1) == 1 and a.shape[1] % heads == 0 and out.shape[1] % heads == 0 and out.shape[0] == T,
+          "gemm_heads: rows must hold whole heads")
+    N, K = w.shape[1], w.shape[2]
+    a_head, o_head = a.shape[1] // heads, out.shape[1] // heads
+    _need(K <= a_head and N <= o_head and a.dtype == w.dtype, "gemm_heads: heads narrower than the product")
+    call("tie_gemm_simt_batched", dtype_code(a), dtype_code(out), a.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K,
+         a.stride(0), K, out.stride(0), heads, a_head, N * K, o_head, _stream())
+
+
+# -- the residual stream beside a second stream, gated units with biases (csrc/stream_glue.cu)
+
+def add_concat(x, delta, other, out) -> None:
+    """x += delta (float32, in place; delta a tensor in out's dtype, a SplitSum, or None), then out[t] = [x[t] | other[t]]."""
+    part = None
+    if isinstance(delta, SplitSum):
+        part, delta = delta, None
+        _need(part.M == x.shape[0] and part.N == x.shape[-1], "add_concat: partial sums do not match x")
+    _dev(x, delta, other, out)
+    T, D = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous() and other.dtype == torch.float32 and other.is_contiguous() and
+          other.shape == x.shape, "add_concat: x and other must be float32 [T, D] contiguous")
+    _need(out.shape == (T, 2 * D) and out.is_contiguous(), "add_concat: out must be [T, 2 D] contiguous")
+    if delta is not None:
+        _need(delta.dtype == out.dtype and delta.shape == x.shape and delta.is_contiguous(), "add_concat: delta must match x's shape and out's dtype")
+    call("tie_add_concat", dtype_code(out), x.data_ptr(), _ptr(delta), part.partial.data_ptr() if part else 0,
+         part.stride if part else 0, part.splits if part else 0, other.data_ptr(), out.data_ptr(), T, D, _stream())
+
+
+ACT_SILU, ACT_GELU_TANH = 0, 1
+
+
+def glu_biased(gate_up, bias_gate, bias_up, out, act: int = ACT_SILU) -> None:
+    """out[t, i] = act(gate_up[t, i] + bias_gate[i]) * (gate_up[t, I + i] + bias_up[i]); out [T, >= I]: a wider out gets a
+    1 in column I and zeros behind it (for a product whose weight carries its bias as column I)."""
+    _dev(gate_up, bias_gate, bias_up, out)
+    T, I = gate_up.shape[0], gate_up.shape[1] // 2
+    _need(gate_up.dim() == 2 and gate_up.shape[1] == 2 * I and gate_up.is_contiguous() and out.is_contiguous() and out.shape[0] == T
+          and out.shape[1] >= I and gate_up.dtype == out.dtype, "glu_biased: gate_up [T, 2I], out [T, >= I], one dtype, contiguous")
+    for b in (bias_gate, bias_up):
+        _need(b is None or (b.dtype == torch.float32 and b.numel() == I), "glu_biased: biases must be float32 [I]")
+    call("tie_glu_biased", dtype_code(out), gate_up.data_ptr(), _ptr(bias_gate), _ptr(bias_up), out.data_ptr(), T, I, out.shape[1],
+         int(act), _stream())
+
+
+# -- experts (csrc/moe.cu)
+
+def moe_route(logits, top: int, groups: int, keep: int, ids, weights) -> None:
+    """Per token: softmax over all experts, the `keep` best of `groups` equal blocks of consecutive experts (a group counts as much
+    as its best member), the `top` best experts of those; ids int32 [T, top], weights float32 [T, top] = the chosen scores
+    over their sum (+ 1e-20)."""
+    _dev(logits, ids, weights)
+    T, E = logits.shape
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "moe_route: logits must be float32 rows")
+    _need(ids.dtype == torch.int32 and ids.is_contiguous() and ids.shape == (T, top) and weights.dtype == torch.float32 and
+          weights.is_contiguous() and weights.shape == (T, top), "moe_route: ids int32 [T, top], weights float32 [T, top]")
+    call("tie_moe_route", logits.data_ptr(), logits.stride(0), T, E, top, groups, keep, ids.data_ptr(), weights.data_ptr(), _stream())
+
+
+def moe_max_tiles(pairs: int, experts: int, block_m: int) -> int:
+    return int(library.library().tie_moe_max_tiles(pairs, experts, block_m))
+
+
+def moe_align(ids, experts: int, block_m: int, sorted_pairs, tile_expert, meta) -> None:
+    """Lists the (token, choice) pairs by expert, each expert's range a whole number of tiles of block_m rows (-1 pads);
+    tile_expert[i] is tile i's expert, meta[0] the number of tiles. All int32, on the device."""
+    _dev(ids, sorted_pairs, tile_expert, meta)
+    pairs = ids.numel()
+    tiles = moe_max_tiles(pairs, experts, block_m)
+    _need(all(t.dtype == torch.int32 and t.is_contiguous() for t in (ids, sorted_pairs, tile_expert, meta)) and
+          sorted_pairs.numel() >= tiles * block_m and tile_expert.numel() >= tiles and meta.numel() >= 1,
+          "moe_align: int32 arrays, sorted_pairs and tile_expert long enough for the most tiles")
+    call("tie_moe_align", ids.data_ptr(), pairs, experts, block_m, sorted_pairs.data_ptr(), tile_expert.data_ptr(), meta.data_ptr(), _stream())
+
+
+def moe_gemm(a, w, out, top: int, block_m: int, sorted_pairs, tile_expert, meta, max_tiles: int, second: bool = False,
+             partial=None, weights=None) -> None:
+    """Grouped products by expert. w [experts, N, K]. First (second False): a [T, K], out [T * top, N] = w[expert] a[token]
+    per pair. Second: a [T * top, K], partial float32 [top, T, N] gets weights[pair] * (w[expert] a[pair])."""
+    _dev(a, w, out, partial, weights, sorted_pairs, tile_expert, meta)
+    _need(w.dim() == 3 and w.is_contiguous() and a.dim() == 2 and a.stride(1) == 1 and a.shape[1] == w.shape[2] and a.dtype == w.dtype,
+          "moe_gemm: w [experts, N, K] contiguous, a [rows, K] of w's dtype")
+    N, K = w.shape[1], w.shape[2]
+    if second:
+        T = a.shape[0] // top
+        _need(partial is not None and partial.dtype == torch.float32 and partial.is_contiguous() and partial.numel() >= top * T * N
+              and weights is not None and weights.dtype == torch.float32 and weights.numel() == T * top,
+              "moe_gemm: the second product needs partial float32 [top, T, N] and weights float32 [T * top]")
+    else:
+        T = a.shape[0]
+        _need(out is not None and out.dim() == 2 and out.stride(1) == 1 and out.shape == (T * top, N) and out.dtype == a.dtype,
+              "moe_gemm: out must be [T * top, N] in a's dtype")
+    call("tie_moe_gemm", dtype_code(a), 1 if second else 0, block_m, a.data_ptr(), a.stride(0), w.data_ptr(), N * K,
+         _ptr(out), out.stride(0) if out is not None else 0, _ptr(partial), T * N if second else 0, _ptr(weights),
+         sorted_pairs.data_ptr(), tile_expert.data_ptr(), meta.data_ptr(), max_tiles, top, N, K, _stream())

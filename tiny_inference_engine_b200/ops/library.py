@@ -40,16 +40,29 @@ _SIGNATURES = {
     "tie_attention_prompt_tma_exact": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
     "tie_attention_prompt_umma": [P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
     "tie_attention_merge": [I, P, P, P, I, I, I, P, I, I, I, P, P],
-    "tie_attention_rows_dv": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
-    "tie_attention_split_dv": [I, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, I, I, P, P],
+    "tie_attention_rows_dv": [I, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P],
+    "tie_attention_split_dv": [I, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, I, I, P, I, P],
     "tie_add_normed_rmsnorm": [I, P, P, P, L, I, P, P, F, F, P, P, F, P, I, I, P],
     "tie_glu_clamped": [I, P, P, I, I, F, F, F, P],
     "tie_sigmoid_gate_mul": [I, P, L, P, L, I, I, P],
     "tie_scale_rows": [P, L, I, I, F, P],
     "tie_qkv_span_prep": [I, P, L, I, I, I, P, P, P, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, I, I, P, P, P],
     "tie_delta_prep": [I, P, L, I, I, I, I, P, P, L, L, P, P, P, I, I, I, I, I, I, F, F, P, P, P, P, P, L, P, P, P],
-    "tie_delta_rule": [I, P, P, P, P, P, L, P, L, L, P, L, I, I, I, P, P, I, I, I, I, I, I, P, P],
+    "tie_delta_rule": [I, P, P, P, P, P, L, P, L, L, P, L, I, I, I, P, P, I, I, I, I, I, I, P, I, I, P],
     "tie_delta_out": [I, P, P, L, P, F, P, I, I, I, P],
+    "tie_gemm_simt_batched": [I, I, P, P, P, I, I, I, L, L, L, I, L, L, L, P],
+    "tie_gla_prep": [I, P, L, I, I, I, I, I, I, I, F, F, P, P, P, P, P, L, P],
+    "tie_ssd_prep": [I, P, L, I, I, I, I, P, P, P, L, L, P, P, P, I, I, I, I, I, I, P, P, P, P, P, P, P, P],
+    "tie_head_norm_gate": [I, P, P, L, P, F, P, I, I, I, I, P],
+    "tie_ssd_out": [I, P, P, P, L, P, P, F, P, I, I, I, I, P],
+    "tie_latent_prep": [I, P, L, I, I, I, I, I, P, P, F, P, P, P, P, P, I, P],
+    "tie_latent_query_rot": [I, P, L, I, I, P, P, P, L, I, I, I, P],
+    "tie_head_gate_mul": [I, P, L, P, L, I, I, I, P],
+    "tie_add_concat": [I, P, P, P, L, I, P, P, I, I, P],
+    "tie_glu_biased": [I, P, P, P, P, I, I, I, I, P],
+    "tie_moe_route": [P, L, I, I, I, I, I, P, P, P],
+    "tie_moe_align": [P, I, I, I, P, P, P, P],
+    "tie_moe_gemm": [I, I, I, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, P],
 }
 
 
@@ -85,6 +98,8 @@ def library() -> ctypes.CDLL:
         lib.tie_attention_decode_limit.argtypes = [c_int]
         lib.tie_gemm_tc2_pairs.restype = c_int
         lib.tie_gemm_tc2_pairs.argtypes = []
+        lib.tie_moe_max_tiles.restype = c_int
+        lib.tie_moe_max_tiles.argtypes = [c_int, c_int, c_int]
         lib.tie_replay_launcher_id.restype = c_int
         lib.tie_replay_launcher_id.argtypes = [ctypes.c_char_p]
         lib.tie_replay_launcher_args.restype = c_int

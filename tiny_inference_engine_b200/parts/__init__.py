@@ -1,8 +1,9 @@
 """The parts a model is assembled from, their registries, and the model built from a description."""
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Block, CacheNeed,
-                   Embedding, FeedForward, Mixer, Norm, OutputHead, Part, PositionEncoding, StateNeed, build_part,
+                   Embedding, FeedForward, Mixer, Norm, OutputHead, Part, PositionEncoding, StateNeed, StreamInput, build_part,
                    register_part, to_compute)
-from . import norm, position, attention, gated_attention, delta, feed_forward, block, embedding  # noqa: F401  (register the built-in kinds)
+from . import (norm, position, attention, gated_attention, delta, feed_forward, block, embedding,  # noqa: F401  (register the built-in kinds)
+               latent_attention, linear_attention, state_space, experts, stream_input)
 from .attention import GQAttention
 from .block import PreNormBlock
 from .embedding import LMHead, TokenEmbedding
@@ -12,6 +13,6 @@ from .norm import RMSNorm
 from .position import NoPositionEncoding, RotaryEncoding
 
 __all__ = ["BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "Block", "CacheNeed",
-           "Embedding", "FeedForward", "Mixer", "Norm", "OutputHead", "Part", "PositionEncoding", "StateNeed", "build_part", "register_part", "to_compute",
+           "Embedding", "FeedForward", "Mixer", "Norm", "OutputHead", "Part", "PositionEncoding", "StateNeed", "StreamInput", "build_part", "register_part", "to_compute",
            "GQAttention", "PreNormBlock", "LMHead", "TokenEmbedding", "SwiGLU", "LayerCache", "Model",
            "expected_tensors", "RMSNorm", "NoPositionEncoding", "RotaryEncoding"]

@@ -22,7 +22,8 @@ from ..weights.loader import TensorNeed
 class CacheNeed:
     """What a mixer wants of the paged cache: keys and values of `kv_heads` x `head_dim` per
     token; kind "full" keeps every token, "window" only the last `window`. `value_dim` is the
-    size of a value head where it differs from a key head's (0: the same)."""
+    size of a value head where it differs from a key head's (0: the same; -1: the cache keeps keys only and
+    the mixer finds a token's value inside its key, as attention over one latent per token does)."""
     kind: str
     kv_heads: int
     head_dim: int
@@ -129,6 +130,16 @@ class OutputHead(Part):
         raise NotImplementedError
 
 
+class StreamInput(Part):
+    """Something that happens to the residual stream itself ahead of a run entry's layer (`RunEntry.before`)."""
+
+    def forward(self, x: torch.Tensor, pending, origin: torch.Tensor, ctx):
+        """x: float32 residual stream [T, D], rewritten in place; pending: a delta not yet added to x (or None), which
+        this part adds first; origin: float32 [T, D], what the embedding part made of the step's tokens. Returns the new
+        pending delta (None when x is complete)."""
+        raise NotImplementedError
+
+
 class Block(Part):
     """The arrangement of mixer, feed-forward and their norms in one layer."""
 
@@ -145,12 +156,13 @@ POSITION_ENCODINGS: dict[str, Callable] = {}
 BLOCKS: dict[str, Callable] = {}
 EMBEDDINGS: dict[str, Callable] = {}
 HEADS: dict[str, Callable] = {}
+STREAM_INPUTS: dict[str, Callable] = {}
 _REGISTRIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "position": POSITION_ENCODINGS,
-               "block": BLOCKS, "embedding": EMBEDDINGS, "head": HEADS}
+               "block": BLOCKS, "embedding": EMBEDDINGS, "head": HEADS, "stream_input": STREAM_INPUTS}
 
 
 def register_part(family: str, kind: str, factory: Callable, replace: bool = False) -> None:
-    """family: mixer | feed_forward | norm | position | block | embedding | head.
+    """family: mixer | feed_forward | norm | position | block | embedding | head | stream_input.
     factory(spec, dtype, prefix="") -> part; a block's factory takes (layer_spec, dtype), a head's
     (spec, dtype, embedding=the model's embedding part)."""
     reg = _REGISTRIES[family]

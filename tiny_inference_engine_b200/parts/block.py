@@ -13,10 +13,11 @@ class PreNormBlock(Block):
     def __init__(self, layer_spec, dtype, prefix: str = ""):
         self.mixer_norm = build_part("norm", layer_spec.mixer_norm, dtype)
         self.mixer = build_part("mixer", layer_spec.mixer, dtype)
-        self.ffn_norm = build_part("norm", layer_spec.ffn_norm, dtype)
-        self.ffn = build_part("feed_forward", layer_spec.ffn, dtype)
+        self.has_ffn = layer_spec.ffn is not None          # a layer may be a mixer alone
+        self.ffn_norm = build_part("norm", layer_spec.ffn_norm, dtype) if self.has_ffn else None
+        self.ffn = build_part("feed_forward", layer_spec.ffn, dtype) if self.has_ffn else None
         self.dtype = dtype
-        self.parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        self.parts = (self.mixer_norm, self.mixer) + ((self.ffn_norm, self.ffn) if self.has_ffn else ())
 
     def needs(self):
         n = {}
@@ -34,6 +35,8 @@ class PreNormBlock(Block):
         h = ctx.ws.rows("block.normed", x.shape[0], x.shape[1], self.dtype)
         self.mixer_norm.add_norm(x, as_delta(pending, self.mixer_norm, ctx, "block.delta"), h)
         mixed = self.mixer.forward(h, ctx, cache, state)
+        if not self.has_ffn:
+            return mixed
         self.ffn_norm.add_norm(x, as_delta(mixed, self.ffn_norm, ctx, "block.delta"), h)
         return self.ffn.forward(h, ctx)
 

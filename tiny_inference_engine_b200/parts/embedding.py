@@ -30,6 +30,27 @@ class TokenEmbedding(Embedding):
         ops.embed(self.table, tokens, x)
 
 
+class NormedTokenEmbedding(TokenEmbedding):
+    """x[t] = norm(table[id]): the looked-up rows pass a norm part (`norm`, a PartSpec of the norm family) before they
+    become the residual stream."""
+
+    def __init__(self, spec, dtype, prefix: str = ""):
+        super().__init__(spec, dtype, prefix)
+        from .base import build_part
+        self.norm = build_part("norm", spec["norm"], torch.float32)
+
+    def needs(self):
+        return {**super().needs(), **self.norm.needs()}
+
+    def bind(self, get):
+        super().bind(get)
+        self.norm.bind(get)
+
+    def forward(self, tokens, x):
+        ops.embed(self.table, tokens, x)
+        self.norm.rows(x, x)            # float32 rows, in place
+
+
 class LMHead(OutputHead):
     def __init__(self, spec, dtype, embedding: TokenEmbedding | None = None, prefix: str = ""):
         self.name = spec["name"]
@@ -60,4 +81,5 @@ class LMHead(OutputHead):
 
 
 register_part("embedding", "token_embedding", TokenEmbedding, replace=True)
+register_part("embedding", "normed_token_embedding", NormedTokenEmbedding, replace=True)
 register_part("head", "lm_head", LMHead, replace=True)

@@ -1,0 +1,96 @@
+"""A feed-forward of many small experts of which each token uses a few.
+
+    s      = softmax(h Wr^T) over all experts                      float32
+    chosen = the `top` experts with the largest s among the experts of the `group_keep` best of `group_count` equal
+             blocks of consecutive experts (a block's score is its best member's; ties go to the lower index)
+    weight = s[chosen] / (sum of s[chosen] + 1e-20)
+    out    = sum over chosen of weight * expert(h)
+    expert = down(g * sigmoid(slope * g) * (u + up_shift)),  g = min(gate(h), limit), u = clamp(up(h), -limit, limit)
+
+The router's product writes float32; routing (softmax, groups, top-k, weights) is one float kernel. Tokens are then
+listed by expert on the device (nothing of a step's routing reaches the host, so decode steps stay captured graphs),
+and two grouped products run over that list, the clamped unit between them. The second product writes
+weight * result as float32 partial sums [top, tokens, hidden], which the block's next residual add sums in order:
+the weighted sum over experts happens in float32 in the residual add itself. What a token computes depends on its
+own experts only, never on what else is in the step. params: `hidden_size`, `intermediate_size`, `num_experts`, `top`,
+`group_count`, `group_keep`, `limit`, `slope`, `up_shift`; tensors `<prefix>router` and `<prefix>e<i>.gate|up|down`.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..errors import InvalidArgument
+from ..weights.loader import TensorNeed
+from .base import FeedForward, register_part, to_compute
+
+
+class RoutedExperts(FeedForward):
+    launches_only = False
+
+    def __init__(self, spec, dtype, prefix: str = ""):
+        p = spec.params
+        self.prefix = prefix + p.get("prefix", "")
+        self.hidden, self.inter = int(p["hidden_size"]), int(p["intermediate_size"])
+        self.experts, self.top = int(p["num_experts"]), int(p["top"])
+        self.group_count, self.group_keep = int(p.get("group_count", 1)), int(p.get("group_keep", 1))
+        self.limit, self.slope, self.up_shift = float(p["limit"]), float(p.get("slope", 1.0)), float(p.get("up_shift", 0.0))
+        E, G = self.experts, self.group_count
+        if min(E, self.top, G, self.group_keep, self.inter) <= 0 or E % G or self.group_keep > G or \
+                self.top > self.group_keep * (E // G) or self.top > 32:
+            raise InvalidArgument(f"experts: cannot choose {self.top} (at most 32) of {E} experts in {G} groups of which "
+                                  f"{self.group_keep} are kept")
+        self.dtype = dtype
+
+    def _expert(self, e: int, leaf: str) -> str:
+        return f"{self.prefix}e{e}.{leaf}"
+
+    def needs(self):
+        n = {self.prefix + "router": TensorNeed((self.experts, self.hidden))}
+        for e in range(self.experts):
+            n[self._expert(e, "gate")] = TensorNeed((self.inter, self.hidden))
+            n[self._expert(e, "up")] = TensorNeed((self.inter, self.hidden))
+            n[self._expert(e, "down")] = TensorNeed((self.hidden, self.inter))
+        return n
+
+    def bind(self, get):
+        E = self.experts
+        router = to_compute(get(self.prefix + "router"), self.dtype)
+        rows = (E + 7) // 8 * 8
+        padded = torch.zeros((rows, self.hidden), dtype=self.dtype, device=router.device)
+        padded[:E] = router
+        self.router = ops.bound_gemm(padded, split_many=False)
+        self.w_router = self.router.w
+        self.router_rows = rows
+        # [experts, 2 * inter, hidden]: an expert's gate rows, then its up rows; [experts, hidden, inter]
+        self.w_gate_up = torch.stack([torch.cat([to_compute(get(self._expert(e, "gate")), self.dtype),
+                                                 to_compute(get(self._expert(e, "up")), self.dtype)], dim=0) for e in range(E)]).contiguous()
+        self.w_down = torch.stack([to_compute(get(self._expert(e, "down")), self.dtype) for e in range(E)]).contiguous()
+
+    def forward(self, h, ctx):
+        T, E, top, I, D = h.shape[0], self.experts, self.top, self.inter, self.hidden
+        logits = ctx.ws.rows("moe.logits", T, self.router_rows, torch.float32)
+        self.router(h, logits)
+        ids = ctx.ws.rows("moe.ids", T, top, torch.int32)
+        weights = ctx.ws.rows("moe.weights", T, top, torch.float32)
+        ops.moe_route(logits[:, :E], top, self.group_count, self.group_keep, ids, weights)
+        pairs = T * top
+        block_m = 16 if pairs <= 16 * E else 64
+        rows_cap = ctx.ws.max_rows * top
+        tiles_cap = max(ops.moe_max_tiles(rows_cap, E, 16), 1)
+        sorted_pairs = ctx.ws.flat("moe.sorted", max(ops.moe_max_tiles(rows_cap, E, 16) * 16, ops.moe_max_tiles(rows_cap, E, 64) * 64), torch.int32)
+        tile_expert = ctx.ws.flat("moe.tile_expert", tiles_cap, torch.int32)
+        meta = ctx.ws.flat("moe.meta", 4, torch.int32)
+        ops.moe_align(ids, E, block_m, sorted_pairs, tile_expert, meta)
+        max_tiles = ops.moe_max_tiles(pairs, E, block_m)
+        gu = ctx.ws.rows("moe.gate_up", T, top * 2 * I, self.dtype).view(pairs, 2 * I)
+        ops.moe_gemm(h, self.w_gate_up, gu, top, block_m, sorted_pairs, tile_expert, meta, max_tiles)
+        act = ctx.ws.rows("moe.act", T, top * I, self.dtype).view(pairs, I)
+        ops.glu_clamped(gu, act, self.limit, self.slope, self.up_shift)
+        partial = ctx.ws.flat("moe.partial", rows_cap * D, torch.float32)
+        ops.moe_gemm(act, self.w_down, None, top, block_m, sorted_pairs, tile_expert, meta, max_tiles, second=True,
+                     partial=partial, weights=weights.view(-1))
+        return ops.SplitSum(partial, top, T, D)
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts, replace=True)

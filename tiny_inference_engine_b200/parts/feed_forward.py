@@ -92,5 +92,61 @@ class ClampedGLU(FeedForward):
         return self.down(act, out, lambda n: ctx.ws.flat("ffn.out.partial", n, torch.float32, self._partial_capacity))
 
 
+class BiasedGLU(FeedForward):
+    """A gated unit whose three products have biases: down(act(gate(h) + b_gate) * (up(h) + b_up)) + b_down, with `act`
+    "silu" or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))). Gate and up are one stacked product; their
+    biases and the activation are one float kernel behind it. The down bias rides in the product: the unit's output
+    gets a column of ones (and zeros up to a multiple of 8) and the weight the bias as that column, so it is added
+    inside the float accumulator and split products still hand on partial sums. params: `hidden_size`,
+    `intermediate_size`, `activation`, and the tensors' names (`gate`, `up`, `down`; biases `<name>.b`) after `prefix`."""
+    launches_only = False
+    ACTIVATIONS = {"silu": ops.ACT_SILU, "gelu_tanh": ops.ACT_GELU_TANH}
+
+    def __init__(self, spec, dtype, prefix: str = ""):
+        p = spec.params
+        self.prefix = prefix + p.get("prefix", "")
+        self.hidden, self.inter = int(p["hidden_size"]), int(p["intermediate_size"])
+        act = p.get("activation", "silu")
+        if act not in self.ACTIVATIONS:
+            from ..errors import UnsupportedError
+            raise UnsupportedError(f"no activation '{act}' (known: {', '.join(sorted(self.ACTIVATIONS))})")
+        self.act = self.ACTIVATIONS[act]
+        self.names = tuple(self.prefix + p.get(k, k) for k in ("gate", "up", "down"))
+        self.padded = (self.inter + 1 + 7) // 8 * 8          # the unit, the column of ones, zeros
+        self.dtype = dtype
+        self._partial_capacity = None
+
+    def needs(self):
+        g, u, d = self.names
+        return {g: TensorNeed((self.inter, self.hidden)), u: TensorNeed((self.inter, self.hidden)),
+                d: TensorNeed((self.hidden, self.inter)), g + ".b": TensorNeed((self.inter,), "norm"),
+                u + ".b": TensorNeed((self.inter,), "norm"), d + ".b": TensorNeed((self.hidden,), "norm")}
+
+    def bind(self, get):
+        g, u, d = self.names
+        gate, up = (to_compute(get(n), self.dtype) for n in (g, u))
+        self.gate_up = ops.bound_gemm(torch.cat([gate, up], dim=0).contiguous(), split_many=False)
+        del gate, up
+        down = to_compute(get(d), self.dtype)
+        wide = torch.zeros((self.hidden, self.padded), dtype=self.dtype, device=down.device)
+        wide[:, :self.inter] = down
+        wide[:, self.inter] = to_compute(get(d + ".b"), self.dtype)
+        self.down = ops.bound_gemm(wide)
+        self.w_gate_up, self.w_down = self.gate_up.w, self.down.w
+        self.bias_gate, self.bias_up = (get(n + ".b").to(torch.float32).contiguous() for n in (g, u))
+
+    def forward(self, h, ctx):
+        T = h.shape[0]
+        gu = ctx.ws.rows("ffn.gate_up", T, 2 * self.inter, self.dtype)
+        self.gate_up(h, gu)
+        act = ctx.ws.rows("ffn.act1", T, self.padded, self.dtype)
+        ops.glu_biased(gu, self.bias_gate, self.bias_up, act, self.act)
+        out = ctx.ws.rows("ffn.out", T, self.hidden, self.dtype)
+        if self._partial_capacity is None:
+            self._partial_capacity = ops.partial_capacity(ctx.ws.max_rows, self.down.N, self.down.K)
+        return self.down(act, out, lambda n: ctx.ws.flat("ffn.out.partial", n, torch.float32, self._partial_capacity))
+
+
 register_part("feed_forward", "swiglu", SwiGLU, replace=True)
+register_part("feed_forward", "biased_glu", BiasedGLU, replace=True)
 register_part("feed_forward", "clamped_glu", ClampedGLU, replace=True)

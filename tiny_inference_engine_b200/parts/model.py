@@ -38,6 +38,16 @@ class Model:
         self.spec, self.dtype = spec, dtype
         self.embedding = build_part("embedding", spec.embedding, dtype)
         self.layers = [_build_block(l, dtype) for l in spec.layers]
+        # What rewrites the residual stream ahead of a run entry (`RunEntry.before`); entries that name the same
+        # part description share one part, and with it its weights.
+        self.stream_inputs: dict[int, object] = {}
+        built: dict[int, object] = {}
+        for i, e in enumerate(spec.run_order):
+            if e.before is not None:
+                if id(e.before) not in built:
+                    built[id(e.before)] = build_part("stream_input", e.before, dtype)
+                self.stream_inputs[i] = built[id(e.before)]
+        self._stream_input_parts = list(built.values())
         self.final_norm = build_part("norm", spec.final_norm, dtype)
         self.head = build_part("head", spec.head, dtype, embedding=self.embedding)
         self.loaded = False
@@ -52,6 +62,8 @@ class Model:
         n = dict(self.embedding.needs())
         for l in self.layers:
             n.update(l.needs())
+        for p in self._stream_input_parts:
+            n.update(p.needs())
         n.update(self.final_norm.needs())
         n.update(self.head.needs())
         return n
@@ -73,6 +85,8 @@ class Model:
         self.embedding.bind(get)
         for l in self.layers:
             l.bind(get)
+        for p in self._stream_input_parts:
+            p.bind(get)
         self.final_norm.bind(get)
         self.head.bind(get)
         self.loaded = True
@@ -99,6 +113,10 @@ class Model:
         ctx.ws_dtype = self.dtype
         x = ctx.ws.rows("model.x", T, D, torch.float32)
         self.embedding.forward(ctx.tokens, x)
+        origin = None
+        if self.stream_inputs:          # parts that mix the embedding back in later read it from a buffer of its own
+            origin = ctx.ws.rows("model.origin", T, D, torch.float32)
+            self.embedding.forward(ctx.tokens, origin)
         pending = None
         order = self.spec.run_order
 
@@ -107,6 +125,8 @@ class Model:
             owner = i if entry.cache_of is None else entry.cache_of
             view = cache.layer_cache(owner, writes=entry.cache_of is None) if cache is not None else None
             state = states.tensor(i) if states is not None else None
+            if i in self.stream_inputs:
+                pending = self.stream_inputs[i].forward(x, pending, origin, ctx)
             pending = self.layers[entry.layer].forward(x, pending, ctx, view, state)
             if ctx.layer_hook is not None:
                 ctx.layer_hook(i, x, pending)
