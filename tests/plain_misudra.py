@@ -53,9 +53,38 @@ def f64(a):
     return np.asarray(a, dtype=np.float64)
 
 
+_act = None       # with `bfloat16_activations()`: rounds what a 16-bit pipeline would keep in 16 bits
+
+
+class bfloat16_activations:
+    """Within this context the outputs of `linear` and of the layers' norms are rounded to bfloat16 (the weights of the
+    tests are bfloat16 values already): the difference to the exact result is the noise that a pipeline with 16-bit
+    activations cannot avoid, which is what a tolerance for such a pipeline is measured against."""
+
+    def __enter__(self):
+        global _act
+        _act = lambda y: round_bf16(y).astype(np.float64)
+
+    def __exit__(self, *exc):
+        global _act
+        _act = None
+
+
 def linear(x, w, b=None):
     y = f64(x) @ f64(w).T
-    return y if b is None else y + f64(b)
+    y = y if b is None else y + f64(b)
+    return y if _act is None else _act(y)
+
+
+def kept(y):
+    """A value that a 16-bit pipeline hands from one kernel to the next (or keeps in its cache)."""
+    return y if _act is None else _act(y)
+
+
+def layer_norm(x, w, eps):
+    """The norm ahead of a sublayer: rms times a plain weight."""
+    y = rms(x, eps) * f64(w)
+    return y if _act is None else _act(y)
 
 
 # --------------------------------------------------------------------------- latent attention
@@ -86,12 +115,12 @@ def latent_attention_mixer(h, w, p, mx, eps, positions):
     H, dim, rot, vdim, R = mx["heads"], mx["dim"], mx["rot_dim"], mx["vdim"], mx["kv_rank"]
     T = h.shape[0]
     base = mx["rot"]["base"]
-    cq = rms(linear(h, w[p + "dq"]), eps) * f64(w[p + "dq.norm"])
+    cq = kept(rms(linear(h, w[p + "dq"]), eps) * f64(w[p + "dq.norm"]))
     q = linear(cq, w[p + "uq"]).reshape(T, H, dim + rot)
     q_plain, q_rot = q[..., :dim], rotate_half(q[..., dim:], positions, rot, base)
     kv = linear(h, w[p + "dkv"])
-    c = rms(kv[:, :R], eps) * f64(w[p + "dkv.norm"])
-    k_rot = rotate_half(kv[:, R:], positions, rot, base)                      # [T, rot], one for all heads
+    c = kept(rms(kv[:, :R], eps) * f64(w[p + "dkv.norm"]))
+    k_rot = kept(rotate_half(kv[:, R:], positions, rot, base))                # [T, rot], one for all heads
     k_plain = linear(c, w[p + "uk"]).reshape(T, H, dim)
     v = linear(c, w[p + "uv"]).reshape(T, H, vdim)
     gate = sigmoid(linear(h, w[p + "g"]))                                      # [T, H]
@@ -99,7 +128,7 @@ def latent_attention_mixer(h, w, p, mx, eps, positions):
     for a in range(H):
         s = (q_plain[:, a] @ k_plain[:, a].T + q_rot[:, a] @ k_rot.T) * mx["scale"]
         out[:, a] = (window_softmax(s, mx["mask"]["size"]) @ v[:, a]) * gate[:, a:a + 1]
-    return linear(out.reshape(T, H * vdim), w[p + "o"])
+    return linear(kept(out.reshape(T, H * vdim)), w[p + "o"])
 
 
 # --------------------------------------------------------------------------- recurrences
@@ -126,7 +155,7 @@ def gla_mixer(h, w, p, mx, eps):
     alpha = (sigmoid(z) ** (1.0 / mx["tau"])).reshape(T, H, dim)
     o = decayed_outer_recurrence(q, k, v, alpha)
     o = rms(o, eps) * f64(w[p + "norm"])                                        # per head, over vdim
-    return linear(o.reshape(T, H * vdim) * silu(linear(h, w[p + "g"])), w[p + "o"])
+    return linear(kept(o.reshape(T, H * vdim) * silu(linear(h, w[p + "g"]))), w[p + "o"])
 
 
 def causal_conv(x, taps_w, bias):
@@ -158,14 +187,14 @@ def mamba2_mixer(h, w, p, mx, eps):
     y = y.reshape(T, inner) * silu(z)
     parts = mx["norm_groups"]
     y = rms(y.reshape(T, parts, inner // parts), eps).reshape(T, inner) * f64(w[p + "norm"])
-    return linear(y, w[p + "o"])
+    return linear(kept(y), w[p + "o"])
 
 
 # --------------------------------------------------------------------------- feed-forwards
 
 def dense_mlp(h, w, p):
     g = gelu_tanh(linear(h, w[p + "gate"], w[p + "gate.b"]))
-    return linear(g * linear(h, w[p + "up"], w[p + "up.b"]), w[p + "down"], w[p + "down.b"])
+    return linear(kept(g * linear(h, w[p + "up"], w[p + "up.b"])), w[p + "down"], w[p + "down.b"])
 
 
 def route(scores, top, group_count, group_keep):
@@ -185,7 +214,7 @@ def route(scores, top, group_count, group_keep):
 def clamped_expert(h, gate, up, down, limit):
     g = np.minimum(linear(h, gate), limit)
     u = np.clip(linear(h, up), -limit, limit)
-    return linear(g * sigmoid(1.702 * g) * (u + 1.0), down)
+    return linear(kept(g * sigmoid(1.702 * g) * (u + 1.0)), down)
 
 
 def moe_mlp(h, w, p, mlp, chosen_out=None):
@@ -234,7 +263,7 @@ def forward(w, cfg, tokens, layers_out=None, routes_out=None):
         if place in starts:
             x = linear(np.concatenate([x, x0], axis=-1), w["loop.in"])
         layer, p = cfg["layers"][i], f"l{i}."
-        h = rms(x, eps) * f64(w[p + "norm1"])
+        h = layer_norm(x, w[p + "norm1"], eps)
         kind = layer["type"]
         if kind == "latent_attention":
             y = latent_attention_mixer(h, w, p + "mix.", layer["mixer"], eps, pos)
@@ -247,11 +276,11 @@ def forward(w, cfg, tokens, layers_out=None, routes_out=None):
         x = x + y
         mlp = layer.get("mlp")
         if mlp is not None:
-            h = rms(x, eps) * f64(w[p + "norm2"])
+            h = layer_norm(x, w[p + "norm2"], eps)
             x = x + (dense_mlp(h, w, p + "mlp.") if mlp["kind"] == "dense" else moe_mlp(h, w, p + "mlp.", mlp, routes_out))
         if layers_out is not None:
             layers_out.append(x.copy())
-    return linear(rms(x, eps) * f64(w["final.norm"]), w["head"])
+    return linear(layer_norm(x, w["final.norm"], eps), w["head"])
 
 
 def generate(w, cfg, prompt, n):
@@ -348,10 +377,13 @@ def round_bf16(x):
     return rounded.astype(np.uint32).view(np.float32).reshape(np.shape(x))
 
 
-def random_weights(cfg, seed, decay_rank=8, sharp=3.0):
+def random_weights(cfg, seed, decay_rank=8, sharp=3.0, expert_gain=1.0):
     """float32 weights that bfloat16 holds exactly (so that both dtypes load the same model). Matrices are
     N(0, 1/in); the query and key paths of attention layers are `sharp` times larger so that attention is not flat
-    and a key that is lost or misplaced moves the logits; routers are larger so that choices are not close calls."""
+    and a key that is lost or misplaced moves the logits. `expert_gain` scales what the experts add to the stream:
+    with random routers some token's choice between two experts is always a close call that 16-bit rounding decides
+    the other way, and a small gain keeps such a flip within a 16-bit tolerance (32-bit runs see the experts to the
+    last digit either way)."""
     rng = np.random.default_rng(seed)
     w = {}
     for name, shape in tensor_shapes(cfg, decay_rank).items():
@@ -378,6 +410,8 @@ def random_weights(cfg, seed, decay_rank=8, sharp=3.0):
                 t = t * 4.0
             if leaf == "a2":
                 t = t * 3.0
+            if leaf == "down" and ".mlp.e" in name:
+                t = t * expert_gain
         w[name] = round_bf16(np.asarray(t, dtype=np.float32))
     return w
 
