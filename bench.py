@@ -191,6 +191,21 @@ def dugazen_config(width, layers, heads, kv_heads, ff, vocab, window=1024, vdim=
             "norm": {"eps": 1e-6}, "residual_mult": 1.0, "vocab": vocab, "width": width}
 
 
+def misudra_config(width, layers, heads, kv_heads, ff, vocab, window=1024):
+    """Latent attention, gated linear attention and state-space layers in turn at the sizes of a Qwen3 layer; feed-forwards
+    dense and routed in turn, the routed one with as many active parameters as the dense one (4 of 32 experts of ff / 4);
+    the second half of the layers runs twice."""
+    dense = {"ff": ff, "kind": "dense"}
+    routed = {"expert": {"ff": ff // 4, "limit": 7.0}, "kind": "moe",
+              "router": {"experts": 32, "groups": {"count": 8, "keep": 4}, "top": 4}}
+    kinds = [{"type": "latent_attention", "mixer": {"dim": 128, "heads": heads, "kv_rank": 512, "mask": {"size": window}, "q_rank": 1536,
+                                                    "rot": {"base": 1000000.0, "dims": 64}, "rot_dim": 64, "scale": 192 ** -0.5, "vdim": 128}},
+             {"type": "gla", "mixer": {"dim": 128, "heads": heads, "tau": 16.0, "vdim": 128}},
+             {"type": "mamba2", "mixer": {"conv": 4, "groups": max(1, heads // 8), "heads": heads, "norm_groups": 1, "state": 128, "vdim": 128}}]
+    return {"architecture": "Misudra", "layers": [dict(kinds[i % 3], mlp=dense if i % 2 == 0 else routed) for i in range(layers)],
+            "loop": {"start": layers // 2, "stop": layers, "times": 2}, "norm": {"eps": 1e-6}, "vocab": vocab, "width": width}
+
+
 DESIGN_SIZES = {     # name: (width, layers, heads, kv heads, feed-forward, vocab)
     "2048x16": (2048, 16, 16, 8, 6144, 151936),
     "4096x8": (4096, 8, 32, 8, 12288, 151936),
@@ -213,9 +228,10 @@ def design_bench(args) -> dict:
         width, layers, heads, kv_heads, ff, vocab = DESIGN_SIZES[size]
         if args.layers:
             layers = args.layers
-        configs = {"dugazen": dugazen_config(width, layers, heads, kv_heads, ff, vocab, vdim=args.design_vdim),
+        configs = {"misudra": misudra_config(width, layers * 2 // 3, heads, kv_heads, ff, vocab)} if args.design == "misudra" else {}
+        configs.update({"dugazen": dugazen_config(width, layers, heads, kv_heads, ff, vocab, vdim=args.design_vdim),
                    "qwen3": dict(QWEN3_8B, hidden_size=width, intermediate_size=ff, num_hidden_layers=layers,
-                                 num_attention_heads=heads, num_key_value_heads=kv_heads, vocab_size=vocab)}
+                                 num_attention_heads=heads, num_key_value_heads=kv_heads, vocab_size=vocab)})
         row = {"size": size, "layers": layers, "width": width, "heads": heads, "kv_heads": kv_heads, "ff": ff}
         for name, config in configs.items():
             if args.design_only and name != args.design_only:
@@ -288,7 +304,9 @@ def design_bench(args) -> dict:
             gc.collect()
             torch.cuda.empty_cache()
         rows.append(row)
-    return {"design": "dugazen", "beside": "qwen3 at equal width, layers, heads and feed-forward", "dtype": "bf16",
+    return {"design": args.design, "beside": ("dugazen and qwen3 at equal width, heads and feed-forward and as many layer runs "
+                                              "(two thirds of the layers, the second half run twice)" if args.design == "misudra" else
+                                              "qwen3 at equal width, layers, heads and feed-forward"), "dtype": "bf16",
             "data": "synthetic (random weights, uniform random token ids)", "prefill_tokens": T, "batch": B, "context": CTX,
             "value_head": args.design_vdim, "window": 1024, "sizes": rows, "clocks": clocks.stop()}
 
@@ -313,11 +331,11 @@ def main() -> int:
     ap.add_argument("--profile", choices=["decode", "prefill", "mixed"], help="run two steps of one kind (mixed: 30 requests "
                     "decoding at context 2,048 beside a 482-token portion of a prompt, the serving default of 512 tokens a step), kernel by kernel, between "
                     "cudaProfilerStart/Stop (for ncu --profile-from-start off) and print no bench line")
-    ap.add_argument("--design", choices=["dugazen"], help="prefill and decode throughput of that design beside Qwen3 at equal "
+    ap.add_argument("--design", choices=["dugazen", "misudra"], help="prefill and decode throughput of that design beside Qwen3 at equal "
                     "sizes (a line of its own; the default workload and its line stay as they are)")
     ap.add_argument("--design-size", choices=sorted(DESIGN_SIZES), help="--design: one size only")
     ap.add_argument("--design-vdim", type=int, default=128, help="--design: size of a value head (keys have 128)")
-    ap.add_argument("--design-only", choices=["dugazen", "qwen3"], help="--design: one of the two models only")
+    ap.add_argument("--design-only", choices=["dugazen", "misudra", "qwen3"], help="--design: one of the two models only")
     args = ap.parse_args()
 
     if args.design:

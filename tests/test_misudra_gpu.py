@@ -528,7 +528,7 @@ def test_grouped_products_against_plain_sums(tokens, dtype):
     w2 = (torch.randn((E, D, I), generator=g) / I ** 0.5).to(dtype).cuda()
     ids = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(tokens)]).to(torch.int32).cuda()
     weights = torch.rand((tokens, top), generator=g).cuda()
-    for block_m in (16, 64):
+    for block_m in (4, 16, 64):
         tiles = ops.moe_max_tiles(tokens * top, E, block_m)
         sorted_pairs = torch.empty(tiles * block_m, dtype=torch.int32, device="cuda")
         tile_expert = torch.empty(tiles, dtype=torch.int32, device="cuda")
@@ -549,3 +549,53 @@ def test_grouped_products_against_plain_sums(tokens, dtype):
         want = torch.stack([torch.stack([weights[t, s] * (w2[int(ids[t, s])].float() @ act[t * top + s].float()) for t in range(tokens)])
                             for s in range(top)])
         assert torch.allclose(partial.view(top, tokens, D), want, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("tokens", [40, 700])
+def test_grouped_products_on_the_tensor_cores(tokens):
+    """bfloat16 prompts: rows copied into the listed order, the grouped products over weights in k-blocks, the weighted
+    results back to their tokens; and the few-rows kernel over the same weights."""
+    from tiny_inference_engine_b200 import ops
+    E, top, D, I = 6, 2, 72, 40
+    g = torch.Generator().manual_seed(tokens)
+    h = torch.randn((tokens, D), generator=g).to(torch.bfloat16).cuda()
+    w1 = (torch.randn((E, 2 * I, D), generator=g) / D ** 0.5).to(torch.bfloat16).cuda()
+    w2 = (torch.randn((E, D, I), generator=g) / I ** 0.5).to(torch.bfloat16).cuda()
+    b1, b2 = ops.pack_k_blocks(w1.view(E * 2 * I, D)), ops.pack_k_blocks(w2.view(E * D, I))
+    ids = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(tokens)]).to(torch.int32).cuda()
+    ids[:, 0] = torch.where(ids[:, 0] == 4, ids[:, 1], ids[:, 0])          # expert 4 mostly idle, some experts busier
+    weights = torch.rand((tokens, top), generator=g).cuda()
+    want1 = torch.stack([w1[int(ids[t, s])].float() @ h[t].float() for t in range(tokens) for s in range(top)])
+    for block_m in (4, ops.GROUPED_TILE):
+        tiles = ops.moe_max_tiles(tokens * top, E, block_m)
+        sorted_pairs = torch.empty(tiles * block_m, dtype=torch.int32, device="cuda")
+        tile_expert = torch.empty(tiles, dtype=torch.int32, device="cuda")
+        meta = torch.zeros(4, dtype=torch.int32, device="cuda")
+        ops.moe_align(ids, E, block_m, sorted_pairs, tile_expert, meta)
+        partial = torch.zeros(top * tokens * D, dtype=torch.float32, device="cuda")
+        if block_m == 4:
+            first = torch.empty((tokens * top, 2 * I), dtype=torch.bfloat16, device="cuda")
+            ops.moe_gemm(h, b1, first, top, 4, sorted_pairs, tile_expert, meta, tiles, blocks_of=(2 * I, D))
+            assert torch.allclose(first.float(), want1, rtol=2e-2, atol=2e-2)
+            act = first[:, :I].contiguous()
+            ops.moe_gemm(act, b2, None, top, 4, sorted_pairs, tile_expert, meta, tiles, second=True, partial=partial,
+                         weights=weights.view(-1), blocks_of=(D, I))
+        else:
+            rows = tiles * block_m
+            xs = torch.full((rows, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+            ops.moe_gather(h, sorted_pairs, meta, top, xs)
+            first = torch.empty((rows, 2 * I), dtype=torch.bfloat16, device="cuda")
+            ops.gemm_grouped(xs, b1, first, 2 * I, D, meta, tile_expert)
+            listed = sorted_pairs[:int(meta[0]) * block_m].cpu().numpy()
+            at = {int(p): r for r, p in enumerate(listed) if p >= 0}
+            order = torch.tensor([at[p] for p in range(tokens * top)], device="cuda")
+            assert torch.allclose(first[order].float(), want1, rtol=2e-2, atol=2e-2)
+            act = first[:, :I].contiguous()
+            y = torch.empty((rows, D), dtype=torch.bfloat16, device="cuda")
+            ops.gemm_grouped(act, b2, y, D, I, meta, tile_expert)
+            ops.moe_combine(y, sorted_pairs, meta, top, weights.view(-1), partial, tokens)
+            act = act[order]
+        torch.cuda.synchronize()
+        want = torch.stack([torch.stack([weights[t, s] * (w2[int(ids[t, s])].float() @ act[t * top + s].float()) for t in range(tokens)])
+                            for s in range(top)])
+        assert torch.allclose(partial.view(top, tokens, D), want, rtol=2e-2, atol=2e-2), f"tiles of {block_m}"

@@ -267,7 +267,8 @@ using namespace tie;
 static int check_attn(const AttnArgs& a, bool any_size = false) {
   TIE_REQUIRE(a.q_heads > 0 && a.kv_heads > 0 && a.q_heads % a.kv_heads == 0,
               "attention: %d query heads are not a multiple of %d kv heads", a.q_heads, a.kv_heads);
-  TIE_REQUIRE(a.head_dim > 0 && a.head_dim <= 512, "attention: head_dim %d must be 1 to 512", a.head_dim);
+  TIE_REQUIRE(a.head_dim > 0 && a.head_dim <= (any_size ? 1024 : 512), "attention: head_dim %d must be 1 to %d", a.head_dim,
+              any_size ? 1024 : 512);
   if (!any_size) {
     TIE_REQUIRE(a.head_dim % 8 == 0, "attention: head_dim %d must be a multiple of 8 and at most 512", a.head_dim);
     TIE_REQUIRE(a.head_dim <= 256 || a.head_dim % 16 == 0, "attention: head_dim %d above 256 must be a multiple of 16",

@@ -63,8 +63,17 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, OutT* __restrict__ out,
                float* __restrict__ partial, long long part_stride, long long ldp, int rows_x, int rows_y, int k_blocks,
                int k_blocks_per_split, long long ldo, int transposed, int silu, int tiles_x, int n_tiles, int* status,
-               int w_rows, int w_row0) {
+               int w_rows, int w_row0, const int* __restrict__ group_meta, const int* __restrict__ group_of_tile) {
   pdl_launch_dependents();   // the next kernel may get resident now; it waits for this one at its own pdl_wait()
+  // Grouped (plain tiling only): the row operand is `group_meta[0]` tiles of 128 rows, fewer than the grid was sized
+  // for, and row tile t multiplies the weight rows of group `group_of_tile[t]` (`rows_y` rows each, one after the
+  // other in the column operand). Both are written by a kernel ahead of this one, so every thread waits for it first.
+  if (group_meta != nullptr) {
+    pdl_wait();
+    const int tiles_y = tiles_x > 0 ? n_tiles / tiles_x : 0;
+    tiles_x = group_meta[0];
+    n_tiles = tiles_x * tiles_y;
+  }
   using C = TcConfig<BN, DEEP>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -111,7 +120,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       uint32_t parity = 1;   // a fresh barrier passes a wait on parity 1
       bool first = true, ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const int i0 = (tile % tiles_x) * kBM, j0 = (tile / tiles_x) * BN;
+        const int i0 = (tile % tiles_x) * kBM;
+        const int j0 = (tile / tiles_x) * BN + (group_of_tile != nullptr ? group_of_tile[tile % tiles_x] * rows_y : 0);
         int kb = kb_begin;
         if (first) {
           first = false;
@@ -363,7 +373,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, long lon
 template <int BN, typename OutT, bool DEEP>
 static int launch_tc(const CUtensorMap& mx, const CUtensorMap& my, void* out, float* partial, long long part_stride,
                      long long ldp, int rows_x, int rows_y, int K, long long ldo, int transposed, int silu, int splits, int w_rows,
-                     int w_row0, cudaStream_t s) {
+                     int w_row0, cudaStream_t s, const int* group_meta = nullptr, const int* group_of_tile = nullptr) {
   using C = TcConfig<BN, DEEP>;
   static bool configured = false;
   if (!configured) {
@@ -385,7 +395,8 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& my, void* out, fl
   const int ctas = DEEP ? (n_tiles * z > sms ? max(1, sms / z) : n_tiles) : n_tiles;
   const dim3 grid(min(ctas, n_tiles), 1, z);
   TIE_LAUNCH((gemm_tc_kernel<BN, OutT, DEEP>), grid, kThreads, C::kSmem, s, mx, my, static_cast<OutT*>(out), partial, part_stride, ldp,
-             rows_x, rows_y, k_blocks, per_split, ldo, transposed, silu, tiles_x, n_tiles, status_word(), w_rows, w_row0);
+             rows_x, rows_y, k_blocks, per_split, ldo, transposed, silu, tiles_x, n_tiles, status_word(), w_rows, w_row0, group_meta,
+             group_of_tile);
   return kOk;
 }
 
@@ -474,4 +485,29 @@ TIE_API int tie_gemm_tc(int out_dtype, const void* a, const void* w, void* out, 
     }
   }
   TIE_RETURN_LAUNCH("gemm_tc");
+}
+
+// Grouped product, plain tiling: a [M_cap, K] holds `meta[0]` tiles of 128 rows (M_cap is what the buffers were sized
+// for); tile t multiplies the N weight rows of group `group_of_tile[t]`, and out[M_cap, N] gets the rows in the same
+// order. w is stored in k-blocks, [ceil(K / 64)][w_rows][64], group g's rows at g * N .. g * N + N - 1 (w_rows = groups * N).
+// meta and group_of_tile live on the device and may be written by the kernel right ahead of this one.
+TIE_API int tie_gemm_tc_grouped(int out_dtype, const void* a, const void* w, void* out, int M_cap, int N, int K, long long lda,
+                                long long ldo, int bn, int w_rows, const int* meta, const int* group_of_tile, cudaStream_t s) {
+  TIE_REQUIRE(M_cap > 0 && M_cap % kBM == 0 && N > 0 && K > 0, "gemm_tc_grouped: bad sizes M=%d (whole tiles of 128) N=%d K=%d", M_cap, N, K);
+  TIE_REQUIRE(K % 8 == 0 && lda % 8 == 0 && w_rows >= N && w_rows % N == 0, "gemm_tc_grouped: K=%d, lda and the weight's %d rows", K, w_rows);
+  TIE_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0, "gemm_tc_grouped: operands must be 16-byte aligned");
+  TIE_REQUIRE(bn == 128 || bn == 256, "gemm_tc_grouped: tile width %d", bn);
+  TIE_REQUIRE(out_dtype == TIE_BF16 || out_dtype == TIE_F32, "gemm_tc_grouped: output dtype code %d", out_dtype);
+  TIE_REQUIRE(meta != nullptr && group_of_tile != nullptr && status_word() != nullptr, "gemm_tc_grouped: no tile list");
+  CUtensorMap mx, my;
+  const long long kb_rows = static_cast<long long>(ceil_div(K, kBK)) * w_rows;
+  TIE_REQUIRE(make_map_bf16(&mx, a, M_cap, K, lda, kBK, kBM) && make_map_bf16(&my, w, kb_rows, kBK, kBK, kBK, bn),
+              "gemm_tc_grouped: cuTensorMapEncodeTiled failed (rows %d, K %d)", M_cap, K);
+  int st = kOk;
+#define TIE_TCG_ARGS mx, my, out, nullptr, 0, N, M_cap, N, K, ldo, 0, 0, 1, w_rows, 0, s, meta, group_of_tile
+  if (bn == 128) st = out_dtype == TIE_BF16 ? launch_tc<128, __nv_bfloat16, true>(TIE_TCG_ARGS) : launch_tc<128, float, true>(TIE_TCG_ARGS);
+  else st = out_dtype == TIE_BF16 ? launch_tc<256, __nv_bfloat16, true>(TIE_TCG_ARGS) : launch_tc<256, float, true>(TIE_TCG_ARGS);
+#undef TIE_TCG_ARGS
+  if (st != kOk) return st;
+  TIE_RETURN_LAUNCH("gemm_tc_grouped");
 }

@@ -7,6 +7,10 @@
 //               that is a whole number of tiles of `block_m` rows, and lists the pairs in that order (-1 pads a
 //               tile). Also says which expert each tile belongs to and how many tiles there are, all on the
 //               device: nothing of a step's routing is read by the host, so a step can be a captured graph.
+//   moe_gemv    the same products for tiles of 4 pairs (decode: an expert has a row or two): a warp per output
+//               column streams the expert's weight row once.
+//   moe_gather, moe_combine   for prompts in bfloat16: rows copied into the listed order ahead of the grouped products
+//               on the tensor cores (gemm_tc.cu, tiles of 128 rows), and the weighted results back to their tokens.
 //   moe_gemm    grouped products on the CUDA cores, one block per (tile of rows, 64 output columns): rows are
 //               gathered through the list, weights are the tile's expert's. `first` reads token rows and writes a
 //               row per pair; `second` reads a row per pair and writes weight * result as the pair's choice-th
@@ -204,9 +208,121 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const TI* __restrict__ a,
   }
 }
 
+// Few rows per expert (decode): tiles of 4 pairs, one warp per (tile, output column). The warp streams its weight row
+// once with 16-byte loads and keeps one sum per pair; the pairs' input rows come from L1/L2. Needs K in whole vectors.
+template <typename TI, typename TO, bool SECOND>
+__global__ void __launch_bounds__(256) moe_gemv_kernel(const TI* __restrict__ a, long long lda, const TI* __restrict__ w,
+                                                       long long w_expert_stride, TO* __restrict__ out, long long ldo,
+                                                       float* __restrict__ partial, long long part_stride,
+                                                       const float* __restrict__ weights, const int* __restrict__ sorted,
+                                                       const int* __restrict__ tile_expert, const int* __restrict__ meta,
+                                                       int top, int N, int K, int w_rows) {
+  pdl_sync();
+  constexpr int V = Vec16<TI>::N, MT = 4;
+  const int tile = blockIdx.y;
+  if (tile >= meta[0]) return;
+  const int lane = threadIdx.x & 31;
+  const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (n >= N) return;
+  int pair[MT];
+  const TI* arow[MT];
+#pragma unroll
+  for (int i = 0; i < MT; ++i) {
+    pair[i] = sorted[tile * MT + i];
+    arow[i] = pair[i] < 0 ? nullptr : a + static_cast<long long>(SECOND ? pair[i] : pair[i] / top) * lda;
+  }
+  // w_rows > 0: the weights are stored in k-blocks, [ceil(K / 64)][w_rows][64], this expert's rows at expert * N
+  const TI* wr = w_rows > 0 ? w + (static_cast<long long>(tile_expert[tile]) * N + n) * 64
+                            : w + static_cast<long long>(tile_expert[tile]) * w_expert_stride + static_cast<long long>(n) * K;
+  const long long kb_stride = static_cast<long long>(w_rows) * 64;
+  float acc[MT] = {};
+  for (int k = lane * V; k < K; k += 32 * V) {
+    Vec16<TI> wv;
+    wv.load(w_rows > 0 ? wr + (k >> 6) * kb_stride + (k & 63) : wr + k);
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      if (arow[i] != nullptr) {
+        Vec16<TI> av;
+        av.load(arow[i] + k);
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc[i] = fmaf(av.v[j], wv.v[j], acc[i]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MT; ++i) {
+    const float v = warp_sum(acc[i]);
+    if (lane == 0 && pair[i] >= 0) {
+      if (SECOND) partial[(pair[i] % top) * part_stride + static_cast<long long>(pair[i] / top) * N + n] = weights[pair[i]] * v;
+      else st(out + static_cast<long long>(pair[i]) * ldo + n, v);
+    }
+  }
+}
+
+// Many rows per expert (prompts): the pairs' input rows are copied into the listed order, so that the grouped product
+// on the tensor cores reads a dense operand whose tiles of 128 rows belong to one expert each; rows that pad a tile
+// are zeros. 16 bytes a thread.
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ h, long long ldh, const int* __restrict__ sorted,
+                                  const int* __restrict__ meta, int block_m, int top, T* __restrict__ out, int width) {
+  pdl_sync();
+  constexpr int V = Vec16<T>::N;
+  const int row = blockIdx.x;
+  if (row >= meta[0] * block_m) return;
+  const int pair = sorted[row];
+  for (int c = threadIdx.x * V; c < width; c += blockDim.x * V) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (pair >= 0) v = *reinterpret_cast<const uint4*>(h + static_cast<long long>(pair / top) * ldh + c);
+    *reinterpret_cast<uint4*>(out + static_cast<long long>(row) * width + c) = v;
+  }
+}
+
+// partial[pair % top][pair / top][:] = weights[pair] * y[row of the pair], float: the listed rows back to their tokens.
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restrict__ sorted, const int* __restrict__ meta,
+                                   int block_m, int top, const float* __restrict__ weights, float* __restrict__ partial,
+                                   long long part_stride, int width) {
+  pdl_sync();
+  const int row = blockIdx.x;
+  if (row >= meta[0] * block_m) return;
+  const int pair = sorted[row];
+  if (pair < 0) return;
+  const float wgt = weights[pair];
+  float* dst = partial + (pair % top) * part_stride + static_cast<long long>(pair / top) * width;
+  const T* src = y + static_cast<long long>(row) * width;
+  for (int c = threadIdx.x * 4; c < width; c += blockDim.x * 4) {
+    float v[4];
+    load4(src + c, v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] *= wgt;
+    store4(dst + c, v);
+  }
+}
+
 }  // namespace tie
 
 using namespace tie;
+
+// h [T, width] -> out [rows, width] in listed order (rows = meta[0] * block_m of at most max_rows). width in whole 16-byte vectors.
+TIE_API int tie_moe_gather(int dtype, const void* h, long long ldh, const int* sorted, const int* meta, int block_m, int top,
+                           void* out, int width, int max_rows, cudaStream_t s) {
+  TIE_REQUIRE(dtype == TIE_BF16 && width % 8 == 0 && ldh % 8 == 0 && reinterpret_cast<uintptr_t>(h) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(out) % 16 == 0,
+              "moe_gather: bfloat16 rows of %d in whole 16-byte vectors", width);
+  if (max_rows <= 0) return kOk;
+  TIE_LAUNCH((moe_gather_kernel<__nv_bfloat16>), max_rows, 128, 0, s, static_cast<const __nv_bfloat16*>(h), ldh, sorted, meta, block_m,
+             top, static_cast<__nv_bfloat16*>(out), width);
+  TIE_RETURN_LAUNCH("moe_gather");
+}
+
+TIE_API int tie_moe_combine(int dtype, const void* y, const int* sorted, const int* meta, int block_m, int top,
+                            const float* weights, float* partial, long long part_stride, int width, int max_rows, cudaStream_t s) {
+  TIE_REQUIRE(dtype == TIE_BF16 && width % 4 == 0, "moe_combine: bfloat16 rows of %d in whole 8-byte pieces", width);
+  if (max_rows <= 0) return kOk;
+  TIE_LAUNCH((moe_combine_kernel<__nv_bfloat16>), max_rows, 128, 0, s, static_cast<const __nv_bfloat16*>(y), sorted, meta, block_m,
+             top, weights, partial, part_stride, width);
+  TIE_RETURN_LAUNCH("moe_combine");
+}
 
 TIE_API int tie_moe_route(const float* logits, long long ld_logits, int tokens, int experts, int top, int groups, int keep,
                           int* ids, float* weights, cudaStream_t s) {
@@ -222,7 +338,8 @@ TIE_API int tie_moe_route(const float* logits, long long ld_logits, int tokens, 
 
 TIE_API int tie_moe_align(const int* ids, int pairs, int experts, int block_m, int* sorted, int* tile_expert, int* meta,
                           cudaStream_t s) {
-  TIE_REQUIRE(experts > 0 && experts <= 4096 && (block_m == 16 || block_m == 64), "moe_align: bad sizes experts=%d block_m=%d", experts, block_m);
+  TIE_REQUIRE(experts > 0 && experts <= 4096 && (block_m == 4 || block_m == 16 || block_m == 64 || block_m == 128),
+              "moe_align: bad sizes experts=%d block_m=%d", experts, block_m);
   if (pairs <= 0) return kOk;
   TIE_LAUNCH(moe_align_kernel, 1, 1024, 2 * experts * sizeof(int), s, ids, pairs, experts, block_m, sorted, tile_expert, meta);
   TIE_RETURN_LAUNCH("moe_align");
@@ -238,7 +355,20 @@ template <typename TI, typename TO>
 static int launch_moe_gemm(int second, int block_m, const void* a, long long lda, const void* w, long long w_expert_stride,
                            void* out, long long ldo, float* partial, long long part_stride, const float* weights,
                            const int* sorted, const int* tile_expert, const int* meta, int max_tiles, int top, int N, int K,
-                           cudaStream_t s) {
+                           int w_rows, cudaStream_t s) {
+  if (block_m == 4) {
+    const dim3 grid(ceil_div(N, 8), max_tiles);
+    if (second) {
+      TIE_LAUNCH((moe_gemv_kernel<TI, TO, true>), grid, 256, 0, s, static_cast<const TI*>(a), lda, static_cast<const TI*>(w),
+                 w_expert_stride, static_cast<TO*>(out), ldo, partial, part_stride, weights, sorted, tile_expert, meta, top, N, K,
+                 w_rows);
+    } else {
+      TIE_LAUNCH((moe_gemv_kernel<TI, TO, false>), grid, 256, 0, s, static_cast<const TI*>(a), lda, static_cast<const TI*>(w),
+                 w_expert_stride, static_cast<TO*>(out), ldo, partial, part_stride, weights, sorted, tile_expert, meta, top, N, K,
+                 w_rows);
+    }
+    TIE_RETURN_LAUNCH("moe_gemv");
+  }
   const dim3 grid(ceil_div(N, 64), max_tiles);
 #define TIE_MOE_CASE(BM, SECOND)                                                                                            \
   TIE_LAUNCH((moe_gemm_kernel<TI, TO, BM, SECOND>), grid, 256, 0, s, static_cast<const TI*>(a), lda, static_cast<const TI*>(w), \
@@ -255,20 +385,28 @@ static int launch_moe_gemm(int second, int block_m, const void* a, long long lda
 }
 
 // second 0: out[pair, :N] = w[expert] a[pair / top]; second 1: partial[pair % top][pair / top][:N] = weights[pair] * (w[expert] a[pair]).
-// w is [experts, N, K] (an expert's rows K apart, experts w_expert_stride apart).
+// w is [experts, N, K] (an expert's rows K apart, experts w_expert_stride apart), or with w_rows > 0 (tiles of 4 rows only)
+// the same rows one expert after the other stored in k-blocks, [ceil(K / 64)][w_rows][64].
 TIE_API int tie_moe_gemm(int dtype, int second, int block_m, const void* a, long long lda, const void* w,
                          long long w_expert_stride, void* out, long long ldo, float* partial, long long part_stride,
                          const float* weights, const int* sorted, const int* tile_expert, const int* meta, int max_tiles,
-                         int top, int N, int K, cudaStream_t s) {
-  TIE_REQUIRE(N > 0 && K > 0 && top > 0 && (block_m == 16 || block_m == 64) && max_tiles >= 0 && max_tiles <= 65535,
+                         int top, int N, int K, int w_rows, cudaStream_t s) {
+  TIE_REQUIRE(w_rows == 0 || (block_m == 4 && w_rows % N == 0), "moe_gemm: weights in k-blocks are read by the tiles of 4 rows only");
+  TIE_REQUIRE(N > 0 && K > 0 && top > 0 && (block_m == 4 || block_m == 16 || block_m == 64) && max_tiles >= 0 && max_tiles <= 65535,
               "moe_gemm: bad sizes N=%d K=%d top=%d block_m=%d tiles=%d", N, K, top, block_m, max_tiles);
   if (max_tiles == 0) return kOk;
+  if (block_m == 4) {
+    const int v = dtype == TIE_BF16 ? 8 : 4;
+    TIE_REQUIRE(K % v == 0 && lda % v == 0 && w_expert_stride % v == 0 && reinterpret_cast<uintptr_t>(a) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(w) % 16 == 0,
+                "moe_gemm: tiles of 4 rows need K=%d and the row strides in whole 16-byte vectors", K);
+  }
   if (dtype == TIE_F32)
     return launch_moe_gemm<float, float>(second, block_m, a, lda, w, w_expert_stride, out, ldo, partial, part_stride, weights, sorted,
-                                         tile_expert, meta, max_tiles, top, N, K, s);
+                                         tile_expert, meta, max_tiles, top, N, K, w_rows, s);
   if (dtype == TIE_BF16)
     return launch_moe_gemm<__nv_bfloat16, __nv_bfloat16>(second, block_m, a, lda, w, w_expert_stride, out, ldo, partial, part_stride,
-                                                         weights, sorted, tile_expert, meta, max_tiles, top, N, K, s);
+                                                         weights, sorted, tile_expert, meta, max_tiles, top, N, K, w_rows, s);
   set_error("unknown dtype code %d", dtype);
   return kBadArgument;
 }

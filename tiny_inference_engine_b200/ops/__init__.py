@@ -859,6 +859,55 @@ def latent_query_rot(q, dim: int, rot: int, inv_freq, positions, folded, rank: i
          folded.data_ptr(), folded.stride(0), rank, heads, T, _stream())
 
 
+def attention_latent_mma_takes(q, k_cache, key_dim: int, rank: int) -> bool:
+    """Whether the tensor-core kernels for attention over one cached row per token take these operands."""
+    return (q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+            and bool(library.library().tie_attention_latent_mma_takes(key_dim, rank)))
+
+
+def _latent_common(q, k_cache, query_start, context_lens, block_tables, heads, key_dim, rank):
+    _need(k_cache.dim() == 4 and k_cache.is_contiguous() and k_cache.shape[1] == 1 and k_cache.shape[3] == key_dim and
+          k_cache.dtype == torch.bfloat16, "latent attention: the key plane must be bfloat16 [pages, 1, page_size, key_dim]")
+    _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= heads * key_dim and q.dtype == torch.bfloat16,
+          "latent attention: q must be bfloat16 [T, heads * key_dim]")
+    S = context_lens.numel()
+    _need(query_start.dtype == torch.int32 and query_start.numel() == S + 1 and context_lens.dtype == torch.int32 and
+          block_tables.dtype == torch.int32 and block_tables.dim() == 2 and block_tables.shape[0] == S and block_tables.is_contiguous(),
+          "latent attention: index tensors must be int32 (query_start [S+1], context_lens [S], block_tables [S, max_blocks])")
+
+
+def attention_latent_prompt(q, k_cache, out, query_start, context_lens, block_tables, n_seqs: int, max_queries: int, heads: int,
+                            key_dim: int, rank: int, scale: float, window: int = 0) -> None:
+    """Attention of the first n_seqs sequences of the step (each brings several tokens; their rows come first) over a
+    keys-only cache: every head reads the same rows of key_dim, a key's first `rank` elements are its value.
+    q [T, heads * key_dim], out [T, heads * rank], bfloat16, on the tensor cores; softmax in float."""
+    _dev(q, k_cache, out, query_start, context_lens, block_tables)
+    _latent_common(q, k_cache, query_start, context_lens, block_tables, heads, key_dim, rank)
+    _need(out.shape == (q.shape[0], heads * rank) and out.is_contiguous() and out.dtype == torch.bfloat16,
+          "latent attention: out must be bfloat16 [T, heads * rank] contiguous")
+    call("tie_attention_latent_prompt", q.data_ptr(), q.stride(0), k_cache.data_ptr(), out.data_ptr(), query_start.data_ptr(),
+         context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], n_seqs, max_queries, heads, key_dim, rank,
+         k_cache.shape[2], int(window), float(scale), _stream())
+
+
+def attention_latent_split(q, k_cache, out, query_start, context_lens, block_tables, heads: int, key_dim: int, rank: int,
+                           scale: float, seq_list, n_list: int, split_keys: int, max_splits: int, scratch, window: int = 0) -> None:
+    """The same for sequences that bring one token each, their keys cut into splits of `split_keys` that are merged in
+    split order; scratch holds attention_split_scratch_floats(n_list, heads, rank, max_splits) floats."""
+    _dev(q, k_cache, out, query_start, context_lens, block_tables, seq_list, scratch)
+    _latent_common(q, k_cache, query_start, context_lens, block_tables, heads, key_dim, rank)
+    _need(out.shape == (q.shape[0], heads * rank) and out.is_contiguous() and out.dtype == torch.bfloat16,
+          "latent attention: out must be bfloat16 [T, heads * rank] contiguous")
+    _need(seq_list.dtype == torch.int32 and seq_list.numel() >= n_list, "latent attention: seq_list must be int32 [n_list]")
+    _need(scratch.dtype == torch.float32 and scratch.numel() >= attention_split_scratch_floats(n_list, heads, rank, max_splits),
+          "latent attention: scratch too small")
+    call("tie_attention_latent_split", q.data_ptr(), q.stride(0), k_cache.data_ptr(), query_start.data_ptr(),
+         context_lens.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], heads, key_dim, rank, k_cache.shape[2],
+         int(window), float(scale), seq_list.data_ptr(), n_list, split_keys, max_splits, scratch.data_ptr(), _stream())
+    call("tie_attention_merge", dtype_code(out), out.data_ptr(), query_start.data_ptr(), context_lens.data_ptr(), heads, rank,
+         int(window), seq_list.data_ptr(), n_list, split_keys, max_splits, scratch.data_ptr(), _stream())
+
+
 def head_gate_mul(y, gate, heads: int, head_size: int) -> None:
     """y[t, h, :] *= sigmoid(gate[t, h]) in place: one gate per head. y [T, heads * head_size], gate [T, heads] (rows may be strided)."""
     _dev(y, gate)
@@ -950,13 +999,22 @@ def moe_align(ids, experts: int, block_m: int, sorted_pairs, tile_expert, meta) 
 
 
 def moe_gemm(a, w, out, top: int, block_m: int, sorted_pairs, tile_expert, meta, max_tiles: int, second: bool = False,
-             partial=None, weights=None) -> None:
+             partial=None, weights=None, blocks_of=None) -> None:
     """Grouped products by expert. w [experts, N, K]. First (second False): a [T, K], out [T * top, N] = w[expert] a[token]
-    per pair. Second: a [T * top, K], partial float32 [top, T, N] gets weights[pair] * (w[expert] a[pair])."""
+    per pair. Second: a [T * top, K], partial float32 [top, T, N] gets weights[pair] * (w[expert] a[pair]). With
+    `blocks_of` = (N, K) and block_m 4, w is the experts' rows one after the other in k-blocks (`pack_k_blocks`)."""
     _dev(a, w, out, partial, weights, sorted_pairs, tile_expert, meta)
-    _need(w.dim() == 3 and w.is_contiguous() and a.dim() == 2 and a.stride(1) == 1 and a.shape[1] == w.shape[2] and a.dtype == w.dtype,
-          "moe_gemm: w [experts, N, K] contiguous, a [rows, K] of w's dtype")
-    N, K = w.shape[1], w.shape[2]
+    w_rows = 0
+    if blocks_of is not None:
+        N, K = blocks_of
+        _need(block_m == 4 and w.dim() == 3 and w.is_contiguous() and w.shape[2] == 64 and w.shape[0] == (K + 63) // 64 and
+              w.shape[1] % N == 0 and a.dim() == 2 and a.stride(1) == 1 and a.shape[1] == K and a.dtype == w.dtype,
+              "moe_gemm: weights in k-blocks of [experts * N, K] go with tiles of 4 rows")
+        w_rows = w.shape[1]
+    else:
+        _need(w.dim() == 3 and w.is_contiguous() and a.dim() == 2 and a.stride(1) == 1 and a.shape[1] == w.shape[2] and a.dtype == w.dtype,
+              "moe_gemm: w [experts, N, K] contiguous, a [rows, K] of w's dtype")
+        N, K = w.shape[1], w.shape[2]
     if second:
         T = a.shape[0] // top
         _need(partial is not None and partial.dtype == torch.float32 and partial.is_contiguous() and partial.numel() >= top * T * N
@@ -968,4 +1026,45 @@ def moe_gemm(a, w, out, top: int, block_m: int, sorted_pairs, tile_expert, meta,
               "moe_gemm: out must be [T * top, N] in a's dtype")
     call("tie_moe_gemm", dtype_code(a), 1 if second else 0, block_m, a.data_ptr(), a.stride(0), w.data_ptr(), N * K,
          _ptr(out), out.stride(0) if out is not None else 0, _ptr(partial), T * N if second else 0, _ptr(weights),
-         sorted_pairs.data_ptr(), tile_expert.data_ptr(), meta.data_ptr(), max_tiles, top, N, K, _stream())
+         sorted_pairs.data_ptr(), tile_expert.data_ptr(), meta.data_ptr(), max_tiles, top, N, K, w_rows, _stream())
+
+
+GROUPED_TILE = 128      # rows of a tile of the grouped product on the tensor cores
+
+
+def moe_gather(h, sorted_pairs, meta, top: int, out) -> None:
+    """out[r] = h[pair(r) // top] for the rows r listed by `moe_align` with tiles of GROUPED_TILE (zeros where a row pads a
+    tile); bfloat16, width in whole 16-byte vectors."""
+    _dev(h, sorted_pairs, meta, out)
+    _need(h.dim() == 2 and h.stride(1) == 1 and out.dim() == 2 and out.is_contiguous() and out.shape[1] == h.shape[1] and
+          h.dtype == torch.bfloat16 and out.dtype == torch.bfloat16, "moe_gather: bfloat16 rows of one width")
+    call("tie_moe_gather", dtype_code(h), h.data_ptr(), h.stride(0), sorted_pairs.data_ptr(), meta.data_ptr(), GROUPED_TILE, top,
+         out.data_ptr(), h.shape[1], out.shape[0], _stream())
+
+
+def moe_combine(y, sorted_pairs, meta, top: int, weights, partial, tokens: int) -> None:
+    """partial[pair % top][pair // top] = weights[pair] * y[row of the pair] (float32 [top, tokens, width])."""
+    _dev(y, sorted_pairs, meta, weights, partial)
+    _need(y.dim() == 2 and y.is_contiguous() and y.dtype == torch.bfloat16 and partial.dtype == torch.float32 and
+          partial.numel() >= top * tokens * y.shape[1] and weights.dtype == torch.float32, "moe_combine: y bfloat16 rows, partial float32 [top, tokens, width]")
+    call("tie_moe_combine", dtype_code(y), y.data_ptr(), sorted_pairs.data_ptr(), meta.data_ptr(), GROUPED_TILE, top,
+         weights.data_ptr(), partial.data_ptr(), tokens * y.shape[1], y.shape[1], y.shape[0], _stream())
+
+
+def gemm_grouped_takes(rows: int, N: int, K: int) -> bool:
+    """Whether the grouped product on the tensor cores takes these sizes (bfloat16, k in whole 16-byte vectors)."""
+    return K % 8 == 0 and N % 8 == 0 and rows % GROUPED_TILE == 0
+
+
+def gemm_grouped(a, w_blocks, out, N: int, K: int, meta, tile_group) -> None:
+    """out[r, :N] = w[group of r's tile] a[r] for the first meta[0] tiles of GROUPED_TILE rows of a; `w_blocks` is the
+    groups' weights one after the other, [groups * N, K], stored in k-blocks (`pack_k_blocks`)."""
+    _dev(a, w_blocks, out, meta, tile_group)
+    _need(a.dim() == 2 and a.stride(1) == 1 and a.shape[1] == K and a.dtype == torch.bfloat16 and a.shape[0] % GROUPED_TILE == 0,
+          "gemm_grouped: a must be bfloat16 [whole tiles, K]")
+    _need(w_blocks.dim() == 3 and w_blocks.is_contiguous() and w_blocks.shape[2] == 64 and w_blocks.shape[0] == (K + 63) // 64 and
+          w_blocks.shape[1] % N == 0 and w_blocks.dtype == torch.bfloat16, "gemm_grouped: weights must be k-blocks of [groups * N, K]")
+    _need(out.dim() == 2 and out.stride(1) == 1 and out.shape == (a.shape[0], N), "gemm_grouped: out must be [rows, N]")
+    bn = 256 if N >= 256 else 128
+    call("tie_gemm_tc_grouped", dtype_code(out), a.data_ptr(), w_blocks.data_ptr(), out.data_ptr(), a.shape[0], N, K, a.stride(0),
+         out.stride(0), bn, w_blocks.shape[1], meta.data_ptr(), tile_group.data_ptr(), _stream())

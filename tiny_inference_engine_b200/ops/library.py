@@ -58,11 +58,16 @@ _SIGNATURES = {
     "tie_latent_prep": [I, P, L, I, I, I, I, I, P, P, F, P, P, P, P, P, I, P],
     "tie_latent_query_rot": [I, P, L, I, I, P, P, P, L, I, I, I, P],
     "tie_head_gate_mul": [I, P, L, P, L, I, I, I, P],
+    "tie_attention_latent_prompt": [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
+    "tie_attention_latent_split": [P, L, P, P, P, P, I, I, I, I, I, I, F, P, I, I, I, P, P],
     "tie_add_concat": [I, P, P, P, L, I, P, P, I, I, P],
     "tie_glu_biased": [I, P, P, P, P, I, I, I, I, P],
     "tie_moe_route": [P, L, I, I, I, I, I, P, P, P],
     "tie_moe_align": [P, I, I, I, P, P, P, P],
-    "tie_moe_gemm": [I, I, I, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, P],
+    "tie_moe_gemm": [I, I, I, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, I, P],
+    "tie_moe_gather": [I, P, L, P, P, I, I, P, I, I, P],
+    "tie_moe_combine": [I, P, P, P, I, I, P, P, L, I, I, P],
+    "tie_gemm_tc_grouped": [I, P, P, P, I, I, I, L, L, I, I, P, P, P],
 }
 
 
@@ -98,6 +103,8 @@ def library() -> ctypes.CDLL:
         lib.tie_attention_decode_limit.argtypes = [c_int]
         lib.tie_gemm_tc2_pairs.restype = c_int
         lib.tie_gemm_tc2_pairs.argtypes = []
+        lib.tie_attention_latent_mma_takes.restype = c_int
+        lib.tie_attention_latent_mma_takes.argtypes = [c_int, c_int]
         lib.tie_moe_max_tiles.restype = c_int
         lib.tie_moe_max_tiles.argtypes = [c_int, c_int, c_int]
         lib.tie_replay_launcher_id.restype = c_int

@@ -63,9 +63,16 @@ class RoutedExperts(FeedForward):
         self.w_router = self.router.w
         self.router_rows = rows
         # [experts, 2 * inter, hidden]: an expert's gate rows, then its up rows; [experts, hidden, inter]
-        self.w_gate_up = torch.stack([torch.cat([to_compute(get(self._expert(e, "gate")), self.dtype),
-                                                 to_compute(get(self._expert(e, "up")), self.dtype)], dim=0) for e in range(E)]).contiguous()
-        self.w_down = torch.stack([to_compute(get(self._expert(e, "down")), self.dtype) for e in range(E)]).contiguous()
+        w_gate_up = torch.stack([torch.cat([to_compute(get(self._expert(e, "gate")), self.dtype),
+                                            to_compute(get(self._expert(e, "up")), self.dtype)], dim=0) for e in range(E)]).contiguous()
+        w_down = torch.stack([to_compute(get(self._expert(e, "down")), self.dtype) for e in range(E)]).contiguous()
+        # bfloat16 with sizes in whole 16-byte vectors: the experts' rows one after the other in k-blocks, the layout
+        # that the tensor-core product streams (prompts) and that the few-rows kernel reads as well (decode)
+        self.in_blocks = self.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inter % 8 == 0 and w_down.is_cuda
+        if self.in_blocks:
+            w_gate_up = ops.pack_k_blocks(w_gate_up.view(E * 2 * self.inter, self.hidden))
+            w_down = ops.pack_k_blocks(w_down.view(E * self.hidden, self.inter))
+        self.w_gate_up, self.w_down = w_gate_up, w_down
 
     def forward(self, h, ctx):
         T, E, top, I, D = h.shape[0], self.experts, self.top, self.inter, self.hidden
@@ -75,21 +82,43 @@ class RoutedExperts(FeedForward):
         weights = ctx.ws.rows("moe.weights", T, top, torch.float32)
         ops.moe_route(logits[:, :E], top, self.group_count, self.group_keep, ids, weights)
         pairs = T * top
-        block_m = 16 if pairs <= 16 * E else 64
+        few = pairs <= 8 * E      # an expert has a few rows: a warp per output column streams its weights once
+        if self.in_blocks:
+            block_m = 4 if few else ops.GROUPED_TILE
+        elif few and D % 4 == 0 and I % 4 == 0 and self.dtype == torch.float32:
+            block_m = 4
+        else:
+            block_m = 16 if pairs <= 16 * E else 64
         rows_cap = ctx.ws.max_rows * top
-        tiles_cap = max(ops.moe_max_tiles(rows_cap, E, 16), 1)
-        sorted_pairs = ctx.ws.flat("moe.sorted", max(ops.moe_max_tiles(rows_cap, E, 16) * 16, ops.moe_max_tiles(rows_cap, E, 64) * 64), torch.int32)
+        tiles_cap = max(ops.moe_max_tiles(rows_cap, E, 4), 1)
+        sorted_pairs = ctx.ws.flat("moe.sorted", max(ops.moe_max_tiles(rows_cap, E, m) * m for m in (4, 16, 64, 128)), torch.int32)
         tile_expert = ctx.ws.flat("moe.tile_expert", tiles_cap, torch.int32)
         meta = ctx.ws.flat("moe.meta", 4, torch.int32)
         ops.moe_align(ids, E, block_m, sorted_pairs, tile_expert, meta)
         max_tiles = ops.moe_max_tiles(pairs, E, block_m)
+        partial = ctx.ws.flat("moe.partial", rows_cap * D, torch.float32)
+        if block_m == ops.GROUPED_TILE:
+            # prompts on the tensor cores: rows copied into the listed order, two grouped products over dense operands,
+            # the weighted results back to their tokens
+            rows = max_tiles * block_m
+            cap = ops.moe_max_tiles(rows_cap, E, block_m) * block_m
+            xs = ctx.ws.flat("moe.listed", cap * D, self.dtype)[:rows * D].view(rows, D)
+            ops.moe_gather(h, sorted_pairs, meta, top, xs)
+            gu = ctx.ws.flat("moe.listed.gate_up", cap * 2 * I, self.dtype)[:rows * 2 * I].view(rows, 2 * I)
+            ops.gemm_grouped(xs, self.w_gate_up, gu, 2 * I, D, meta, tile_expert)
+            act = ctx.ws.flat("moe.listed.act", cap * I, self.dtype)[:rows * I].view(rows, I)
+            ops.glu_clamped(gu, act, self.limit, self.slope, self.up_shift)
+            y = xs                                          # the listed inputs are done with
+            ops.gemm_grouped(act, self.w_down, y, D, I, meta, tile_expert)
+            ops.moe_combine(y, sorted_pairs, meta, top, weights.view(-1), partial, T)
+            return ops.SplitSum(partial, top, T, D)
         gu = ctx.ws.rows("moe.gate_up", T, top * 2 * I, self.dtype).view(pairs, 2 * I)
-        ops.moe_gemm(h, self.w_gate_up, gu, top, block_m, sorted_pairs, tile_expert, meta, max_tiles)
+        ops.moe_gemm(h, self.w_gate_up, gu, top, block_m, sorted_pairs, tile_expert, meta, max_tiles,
+                     blocks_of=(2 * I, D) if self.in_blocks else None)
         act = ctx.ws.rows("moe.act", T, top * I, self.dtype).view(pairs, I)
         ops.glu_clamped(gu, act, self.limit, self.slope, self.up_shift)
-        partial = ctx.ws.flat("moe.partial", rows_cap * D, torch.float32)
         ops.moe_gemm(act, self.w_down, None, top, block_m, sorted_pairs, tile_expert, meta, max_tiles, second=True,
-                     partial=partial, weights=weights.view(-1))
+                     partial=partial, weights=weights.view(-1), blocks_of=(D, I) if self.in_blocks else None)
         return ops.SplitSum(partial, top, T, D)
 
 

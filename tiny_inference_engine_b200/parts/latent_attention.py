@@ -25,6 +25,9 @@ from .attention import MAX_SPLITS, SPLIT_KEYS
 from .base import CacheNeed, Mixer, build_part, register_part, to_compute
 
 
+LATENT_SPLIT_KEYS = 128     # keys per split of a sequence that brings one token (two key tiles of the tensor-core kernel)
+
+
 def _up8(n: int) -> int:
     return (n + 7) // 8 * 8
 
@@ -46,8 +49,9 @@ class LatentAttention(Mixer):
         if min(self.heads, self.dim, self.vdim, self.rank, self.q_rank) <= 0 or self.rot < 0 or self.rot % 2:
             raise InvalidArgument(f"latent attention: bad sizes heads={self.heads} dim={self.dim} rot={self.rot} vdim={self.vdim} "
                                   f"ranks={self.rank}, {self.q_rank}")
-        if self.rank + self.rot > 512:
-            raise InvalidArgument(f"latent attention: a cached row of {self.rank} + {self.rot} is longer than the 512 the kernels take")
+        if self.rank > 512 or self.rank + self.rot > 1024:
+            raise InvalidArgument(f"latent attention: a latent of {self.rank} (at most 512) with a rotated part of {self.rot} (together at "
+                                  f"most 1024) is more than the kernels take")
         self.dtype = dtype
         self.position = build_part("position", p["position"], dtype, prefix=self.prefix) if self.rot else None
         if self.position is not None:
@@ -133,9 +137,25 @@ class LatentAttention(Mixer):
         return self.gemm_o(attn, out, lambda m: ctx.ws.flat("mixer.out.partial", m, torch.float32, self._capacity))
 
     def _attend(self, folded, mixed, ctx, g, cache):
-        """One kv head of `key_dim` for all query heads; a value is the first `rank` elements of its key."""
+        """One kv head of `key_dim` for all query heads; a value is the first `rank` elements of its key. bfloat16 with
+        sizes in whole MMA steps runs on the tensor cores, everything else (float32 above all) on the CUDA cores."""
         H = self.heads
         n = ctx.multi_rows
+        if ops.attention_latent_mma_takes(folded, cache.k, self.key_dim, self.rank):
+            if n > 0:
+                ops.attention_latent_prompt(folded, cache.k, mixed, ctx.query_start, ctx.context_lens, g.block_tables, ctx.multi_seqs,
+                                            ctx.multi_max_queries, H, self.key_dim, self.rank, self.scale, self.window)
+            if ctx.single_count > 0:
+                longest = ctx.single_max_context if self.window <= 0 else min(ctx.single_max_context, self.window)
+                split_keys = LATENT_SPLIT_KEYS
+                while math.ceil(longest / split_keys) > MAX_SPLITS:
+                    split_keys *= 2
+                max_splits = max(1, math.ceil(longest / split_keys))
+                scratch = ctx.ws.flat("lattn.split", ops.attention_split_scratch_floats(ctx.max_seqs, H, self.rank, MAX_SPLITS), torch.float32)
+                ops.attention_latent_split(folded, cache.k, mixed, ctx.query_start, ctx.context_lens, g.block_tables, H, self.key_dim,
+                                           self.rank, self.scale, ctx.single_seqs, ctx.single_count, split_keys, max_splits, scratch,
+                                           self.window)
+            return
         if n > 0:
             ops.attention_rows_dv(folded[:n], cache.k, cache.k, mixed[:n], ctx.seq_of_row[:n], ctx.query_start, ctx.context_lens,
                                   g.block_tables, H, 1, self.key_dim, self.rank, self.scale, self.window, values_in_keys=True)
