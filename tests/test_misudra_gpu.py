@@ -599,3 +599,20 @@ def test_grouped_products_on_the_tensor_cores(tokens):
         want = torch.stack([torch.stack([weights[t, s] * (w2[int(ids[t, s])].float() @ act[t * top + s].float()) for t in range(tokens)])
                             for s in range(top)])
         assert torch.allclose(partial.view(top, tokens, D), want, rtol=2e-2, atol=2e-2), f"tiles of {block_m}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(5, 3, 24, 40, 8), (300, 4, 64, 96, 32), (130, 2, 10, 6, 0), (1000, 16, 128, 64, 64)])
+def test_products_batched_over_heads(shape, dtype):
+    """out[t, h, :N] = w[h] a[t, h, :K] with the heads side by side in a row and room behind each head's result."""
+    from tiny_inference_engine_b200 import ops
+    T, H, N, K, room = shape
+    g = torch.Generator().manual_seed(T)
+    a = torch.randn((T, H * (K + 8)), generator=g).to(dtype).cuda()
+    w = (torch.randn((H, N, K), generator=g) / K ** 0.5).to(dtype).cuda()
+    out = torch.zeros((T, H * (N + room)), dtype=dtype, device="cuda")
+    ops.gemm_heads(a, w, out, H)
+    want = torch.einsum("thk,hnk->thn", a.view(T, H, K + 8)[:, :, :K].float(), w.float())
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    assert torch.allclose(out.view(T, H, N + room)[:, :, :N].float(), want, rtol=tol, atol=tol)
+    assert (out.view(T, H, N + room)[:, :, N:] == 0).all()                  # what lies behind a head's result is left alone

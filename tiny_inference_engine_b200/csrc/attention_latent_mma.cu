@@ -91,18 +91,31 @@ __global__ void __launch_bounds__(kLatThreads) latent_attention_mma_kernel(Laten
     const __nv_bfloat16* src = valid ? a.q + static_cast<long long>(t0 + tok) * a.q_stride + static_cast<long long>(head) * kd + c * 8 : a.q;
     cp_async16(q_tile + lat_at(r, c, sc), src, valid ? 16 : 0);
   }
-  auto fetch = [&](int key0, uint32_t dst) {
-    for (int i = threadIdx.x; i < kLatKeys * ch; i += kLatThreads) {
-      const int r = i / ch, c = i - r * ch;
-      const int key = key0 + r;
-      const bool valid = key >= key_lo && key <= key_hi;
-      const __nv_bfloat16* src = a.keys;
-      if (valid) src += (static_cast<long long>(table[key / a.page_size]) * a.page_size + key % a.page_size) * kd + c * 8;
-      cp_async16(dst + lat_at(r, c, sc), src, valid ? 16 : 0);
+  // Where each key of a tile lives (element offset of its row in the plane, or -1 outside the CTA's range) is worked
+  // out by 64 threads a tile ahead of the copy that uses it, so that the copy loop has no division and no load that
+  // an address depends on: warp w copies keys w, w + 8, ..., lane l the pieces l, l + 32, ...
+  long long* row_off = reinterpret_cast<long long*>(sbuf + kLatRows * kSLd);         // [2][kLatKeys]
+  auto locate = [&](int tile) {
+    if (threadIdx.x < kLatKeys) {
+      const int key = tile * kLatKeys + threadIdx.x;
+      long long off = -1;
+      if (key >= key_lo && key <= key_hi) off = (static_cast<long long>(table[key / a.page_size]) * a.page_size + key % a.page_size) * kd;
+      row_off[(tile & 1) * kLatKeys + threadIdx.x] = off;
+    }
+  };
+  auto fetch = [&](int tile, uint32_t dst) {
+    const long long* off = row_off + (tile & 1) * kLatKeys;
+    for (int r = warp; r < kLatKeys; r += kLatThreads / 32) {
+      const long long o = off[r];
+      const __nv_bfloat16* src = o >= 0 ? a.keys + o : a.keys;
+      for (int c = lane; c < ch; c += 32) cp_async16(dst + lat_at(r, c, sc), src + (o >= 0 ? c * 8 : 0), o >= 0 ? 16 : 0);
     }
   };
   const int first_tile = key_lo / kLatKeys, last_tile = key_hi / kLatKeys;
-  fetch(first_tile * kLatKeys, k_tile0);
+  locate(first_tile);
+  locate(first_tile + 1);
+  __syncthreads();
+  fetch(first_tile, k_tile0);
   cp_async_commit();
 
   // this thread's two rows: g and g + 8 of its row group
@@ -129,17 +142,37 @@ __global__ void __launch_bounds__(kLatThreads) latent_attention_mma_kernel(Laten
     const uint32_t k_tile = k_tile0 + ((tile - first_tile) & 1) * k_bytes;
     cp_async_wait<0>();
     __syncthreads();                                       // this tile is there; everyone is through with the other buffer and with S
-    if (tile < last_tile) fetch((tile + 1) * kLatKeys, k_tile0 + ((tile + 1 - first_tile) & 1) * k_bytes);
+    if (tile < last_tile) fetch(tile + 1, k_tile0 + ((tile + 1 - first_tile) & 1) * k_bytes);
     cp_async_commit();
+    locate(tile + 2);                                      // read by the copy that the next round issues, behind its barrier
     // 1. scores of keys [16 cg, 16 cg + 16) for this row group
-    float sc4[2][4] = {};
-    for (int ks = 0; ks < (kd >> 4); ++ks) {
+    float sc4[2][4] = {}, sc4b[2][4] = {};                 // two sets of sums in turn: twice as many MMAs in flight
+    const uint32_t q_row = q_tile + lat_at(rg * 16 + (lane & 15), lane >> 4, sc);
+    const uint32_t k_row = k_tile + lat_at(cg * 16 + (lane & 7) + ((lane >> 4) << 3), (lane >> 3) & 1, sc);
+    const int ksteps = kd >> 4;
+    int ks = 0;
+    for (; ks + 1 < ksteps; ks += 2) {
+      uint32_t qa[4], kb[4], qa2[4], kb2[4];
+      ldmatrix_x4(qa, q_row + (ks << 5));
+      ldmatrix_x4(kb, k_row + (ks << 5));
+      ldmatrix_x4(qa2, q_row + ((ks + 1) << 5));
+      ldmatrix_x4(kb2, k_row + ((ks + 1) << 5));
+      mma_bf16(sc4[0], qa, kb[0], kb[1]);
+      mma_bf16(sc4[1], qa, kb[2], kb[3]);
+      mma_bf16(sc4b[0], qa2, kb2[0], kb2[1]);
+      mma_bf16(sc4b[1], qa2, kb2[2], kb2[3]);
+    }
+    if (ks < ksteps) {
       uint32_t qa[4], kb[4];
-      ldmatrix_x4(qa, q_tile + lat_at(rg * 16 + (lane & 15), ks * 2 + (lane >> 4), sc));
-      ldmatrix_x4(kb, k_tile + lat_at(cg * 16 + (lane & 7) + ((lane >> 4) << 3), ks * 2 + ((lane >> 3) & 1), sc));
+      ldmatrix_x4(qa, q_row + (ks << 5));
+      ldmatrix_x4(kb, k_row + (ks << 5));
       mma_bf16(sc4[0], qa, kb[0], kb[1]);
       mma_bf16(sc4[1], qa, kb[2], kb[3]);
     }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sc4[nt][e] += sc4b[nt][e];
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
       float* dst = sbuf + (rg * 16 + g) * kSLd + cg * 16 + nt * 8 + 2 * tq;
@@ -255,7 +288,8 @@ __global__ void __launch_bounds__(kLatThreads) latent_attention_mma_kernel(Laten
 
 static size_t latent_smem(int kd) {
   const int sc = (kd / 8) | 1;
-  return static_cast<size_t>(kLatRows + 2 * kLatKeys) * sc * 16 + static_cast<size_t>(kLatRows) * (kLatKeys + 4) * sizeof(float);
+  return static_cast<size_t>(kLatRows + 2 * kLatKeys) * sc * 16 + static_cast<size_t>(kLatRows) * (kLatKeys + 4) * sizeof(float) +
+         2 * kLatKeys * sizeof(long long);
 }
 
 template <bool SPLIT>

@@ -917,10 +917,14 @@ def head_gate_mul(y, gate, heads: int, head_size: int) -> None:
     call("tie_head_gate_mul", dtype_code(y), y.data_ptr(), y.stride(0), gate.data_ptr(), gate.stride(0), T, heads, head_size, _stream())
 
 
+HEADS_MMA_MIN_ROWS = 16     # up to this many tokens the CUDA-core kernel streams each head's weights once
+
+
 def gemm_heads(a, w, out, heads: int) -> None:
     """out[t, h, :] = w[h] a[t, h, :] for every head: a [T, >= heads * K] with head h at column h * a_head (a_head =
     a.shape[1] // heads), w [heads, N, K] contiguous, out [T, heads * out_head] with the result in the first N
-    columns of each head. Float accumulation on the CUDA cores; a and w of one dtype."""
+    columns of each head. Float accumulation; a and w of one dtype. bfloat16 with more than a few tokens and sizes in
+    whole vectors runs on the tensor cores, everything else on the CUDA cores."""
     _dev(a, w, out)
     T = a.shape[0]
     _need(a.dim() == 2 and out.dim() == 2 and w.dim() == 3 and w.is_contiguous() and w.shape[0] == heads, "gemm_heads: a, out 2-D, w [heads, N, K]")
@@ -929,6 +933,12 @@ def gemm_heads(a, w, out, heads: int) -> None:
     N, K = w.shape[1], w.shape[2]
     a_head, o_head = a.shape[1] // heads, out.shape[1] // heads
     _need(K <= a_head and N <= o_head and a.dtype == w.dtype, "gemm_heads: heads narrower than the product")
+    if (T > HEADS_MMA_MIN_ROWS and a.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and
+            library.library().tie_gemm_heads_mma_takes(a.data_ptr(), a.stride(0), a_head, w.data_ptr(), out.data_ptr(), out.stride(0),
+                                                       o_head, N, K)):
+        call("tie_gemm_heads_mma", a.data_ptr(), a.stride(0), a_head, w.data_ptr(), out.data_ptr(), out.stride(0), o_head, T, N, K,
+             heads, _stream())
+        return
     call("tie_gemm_simt_batched", dtype_code(a), dtype_code(out), a.data_ptr(), w.data_ptr(), out.data_ptr(), T, N, K,
          a.stride(0), K, out.stride(0), heads, a_head, N * K, o_head, _stream())
 

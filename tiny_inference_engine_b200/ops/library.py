@@ -67,6 +67,7 @@ _SIGNATURES = {
     "tie_moe_gemm": [I, I, I, P, L, P, L, P, L, P, L, P, P, P, P, I, I, I, I, I, P],
     "tie_moe_gather": [I, P, L, P, P, I, I, P, I, I, P],
     "tie_moe_combine": [I, P, P, P, I, I, P, P, L, I, I, P],
+    "tie_gemm_heads_mma": [P, L, I, P, P, L, I, I, I, I, I, P],
     "tie_gemm_tc_grouped": [I, P, P, P, I, I, I, L, L, I, I, P, P, P],
 }
 
@@ -105,6 +106,8 @@ def library() -> ctypes.CDLL:
         lib.tie_gemm_tc2_pairs.argtypes = []
         lib.tie_attention_latent_mma_takes.restype = c_int
         lib.tie_attention_latent_mma_takes.argtypes = [c_int, c_int]
+        lib.tie_gemm_heads_mma_takes.restype = c_int
+        lib.tie_gemm_heads_mma_takes.argtypes = [P, L, I, P, P, L, I, I, I]
         lib.tie_moe_max_tiles.restype = c_int
         lib.tie_moe_max_tiles.argtypes = [c_int, c_int, c_int]
         lib.tie_replay_launcher_id.restype = c_int
