@@ -114,7 +114,7 @@ def window_softmax(scores, window):
 def latent_attention_mixer(h, w, p, mx, eps, positions):
     H, dim, rot, vdim, R = mx["heads"], mx["dim"], mx["rot_dim"], mx["vdim"], mx["kv_rank"]
     T = h.shape[0]
-    base = mx["rot"]["base"]
+    base = mx["rot"]["base"] if rot else 1.0
     cq = kept(rms(linear(h, w[p + "dq"]), eps) * f64(w[p + "dq.norm"]))
     q = linear(cq, w[p + "uq"]).reshape(T, H, dim + rot)
     q_plain, q_rot = q[..., :dim], rotate_half(q[..., dim:], positions, rot, base)
@@ -303,11 +303,12 @@ def moe(ff=24, experts=8, top=2, groups=4, keep=2, limit=1.5):
 
 
 def latent_layer(heads=4, dim=16, rot_dim=8, vdim=24, kv_rank=40, q_rank=48, window=24, base=10000.0, scale=None, mlp="dense"):
-    return {"type": "latent_attention",
-            "mixer": {"dim": dim, "heads": heads, "kv_rank": kv_rank, "mask": {"size": window}, "q_rank": q_rank,
-                      "rot": {"base": base, "dims": rot_dim}, "rot_dim": rot_dim,
-                      "scale": scale if scale is not None else (dim + rot_dim) ** -0.5, "vdim": vdim},
-            "mlp": dense() if mlp == "dense" else mlp}
+    mixer = {"dim": dim, "heads": heads, "kv_rank": kv_rank, "mask": {"size": window}, "q_rank": q_rank,
+             "rot": {"base": base, "dims": rot_dim}, "rot_dim": rot_dim,
+             "scale": scale if scale is not None else (dim + rot_dim) ** -0.5, "vdim": vdim}
+    if rot_dim == 0:
+        del mixer["rot"]                # nothing is rotated: the configuration need not say how
+    return {"type": "latent_attention", "mixer": mixer, "mlp": dense() if mlp == "dense" else mlp}
 
 
 def gla_layer(heads=2, dim=24, vdim=16, tau=8.0, mlp="dense"):

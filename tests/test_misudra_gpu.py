@@ -142,6 +142,8 @@ SINGLE = {
     "latent_attention": plain.make_config([L(mlp=None)]),
     "latent_attention_window_out_of_reach_no_gate_effect": plain.make_config([L(heads=2, dim=8, rot_dim=16, vdim=8, kv_rank=24, q_rank=16, window=500, mlp=None)]),
     "latent_attention_sizes_in_whole_pieces": plain.make_config([L(heads=8, dim=64, rot_dim=32, vdim=64, kv_rank=96, q_rank=64, window=30, mlp=None)], width=128),
+    "latent_attention_more_heads_than_a_tile_has_rows": plain.make_config([L(heads=40, dim=16, rot_dim=16, vdim=8, kv_rank=32, q_rank=32, window=20, mlp=None)]),
+    "latent_attention_no_rotated_part": plain.make_config([L(heads=2, dim=16, rot_dim=0, vdim=8, kv_rank=32, q_rank=24, window=12, mlp=None)]),
     "gla": plain.make_config([G(mlp=None)]),
     "gla_fast_decay": plain.make_config([G(heads=3, dim=8, vdim=40, tau=0.5, mlp=None)]),
     "mamba2": plain.make_config([M(mlp=None)]),

@@ -236,9 +236,8 @@ __global__ void __launch_bounds__(256) moe_gemv_kernel(const TI* __restrict__ a,
                             : w + static_cast<long long>(tile_expert[tile]) * w_expert_stride + static_cast<long long>(n) * K;
   const long long kb_stride = static_cast<long long>(w_rows) * 64;
   float acc[MT] = {};
-  for (int k = lane * V; k < K; k += 32 * V) {
-    Vec16<TI> wv;
-    wv.load(w_rows > 0 ? wr + (k >> 6) * kb_stride + (k & 63) : wr + k);
+  auto weight_at = [&](int k) { return w_rows > 0 ? wr + (k >> 6) * kb_stride + (k & 63) : wr + k; };
+  auto step = [&](const Vec16<TI>& wv, int k) {
 #pragma unroll
     for (int i = 0; i < MT; ++i) {
       if (arow[i] != nullptr) {
@@ -248,6 +247,23 @@ __global__ void __launch_bounds__(256) moe_gemv_kernel(const TI* __restrict__ a,
         for (int j = 0; j < V; ++j) acc[i] = fmaf(av.v[j], wv.v[j], acc[i]);
       }
     }
+  };
+  int k = lane * V;
+  for (; k + 3 * 32 * V < K; k += 4 * 32 * V) {          // four weight vectors of the stream in flight a lane
+    Vec16<TI> w0, w1, w2, w3;
+    w0.load(weight_at(k));
+    w1.load(weight_at(k + 32 * V));
+    w2.load(weight_at(k + 2 * 32 * V));
+    w3.load(weight_at(k + 3 * 32 * V));
+    step(w0, k);
+    step(w1, k + 32 * V);
+    step(w2, k + 2 * 32 * V);
+    step(w3, k + 3 * 32 * V);
+  }
+  for (; k < K; k += 32 * V) {
+    Vec16<TI> wv;
+    wv.load(weight_at(k));
+    step(wv, k);
   }
 #pragma unroll
   for (int i = 0; i < MT; ++i) {

@@ -25,6 +25,9 @@ from ..weights.loader import TensorNeed
 from .base import FeedForward, register_part, to_compute
 
 
+ROUTER_SIMT_ROWS = 16      # up to this many tokens the router's product runs on the CUDA cores (it is a few hundred KB)
+
+
 class RoutedExperts(FeedForward):
     launches_only = False
 
@@ -59,7 +62,7 @@ class RoutedExperts(FeedForward):
         rows = (E + 7) // 8 * 8
         padded = torch.zeros((rows, self.hidden), dtype=self.dtype, device=router.device)
         padded[:E] = router
-        self.router = ops.bound_gemm(padded, split_many=False)
+        self.router = ops.bound_gemm(padded, split_many=False, pack=False)     # row-major: few tokens read it on the CUDA cores
         self.w_router = self.router.w
         self.router_rows = rows
         # [experts, 2 * inter, hidden]: an expert's gate rows, then its up rows; [experts, hidden, inter]
@@ -77,7 +80,10 @@ class RoutedExperts(FeedForward):
     def forward(self, h, ctx):
         T, E, top, I, D = h.shape[0], self.experts, self.top, self.inter, self.hidden
         logits = ctx.ws.rows("moe.logits", T, self.router_rows, torch.float32)
-        self.router(h, logits)
+        if T <= ROUTER_SIMT_ROWS:
+            ops.gemm_simt(h, self.w_router, logits)         # a warp per expert streams its row: a few microseconds
+        else:
+            self.router(h, logits)
         ids = ctx.ws.rows("moe.ids", T, top, torch.int32)
         weights = ctx.ws.rows("moe.weights", T, top, torch.float32)
         ops.moe_route(logits[:, :E], top, self.group_count, self.group_keep, ids, weights)

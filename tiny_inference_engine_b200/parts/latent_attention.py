@@ -25,7 +25,8 @@ from .attention import MAX_SPLITS, SPLIT_KEYS
 from .base import CacheNeed, Mixer, build_part, register_part, to_compute
 
 
-LATENT_SPLIT_KEYS = 128     # keys per split of a sequence that brings one token (two key tiles of the tensor-core kernel)
+LATENT_SPLIT_KEYS = 128     # keys per split of a sequence that brings one token (two key tiles of the tensor-core kernel; shorter
+                            # splits cost the merge more than they save the split kernel)
 
 
 def _up8(n: int) -> int:
