@@ -7,8 +7,9 @@
 //               that is a whole number of tiles of `block_m` rows, and lists the pairs in that order (-1 pads a
 //               tile). Also says which expert each tile belongs to and how many tiles there are, all on the
 //               device: nothing of a step's routing is read by the host, so a step can be a captured graph.
-//   moe_gemv    the same products for tiles of 4 pairs (decode: an expert has a row or two): a warp per output
-//               column streams the expert's weight row once.
+//   moe_gemv, moe_gemv_blocks   the same products for tiles of 4 pairs (decode: an expert has a row or two): the
+//               expert's weight rows are streamed once, a warp per output column (row-major weights) or per four
+//               columns (weights in k-blocks).
 //   moe_gather, moe_combine   for prompts in bfloat16: rows copied into the listed order ahead of the grouped products
 //               on the tensor cores (gemm_tc.cu, tiles of 128 rows), and the weighted results back to their tokens.
 //   moe_gemm    grouped products on the CUDA cores, one block per (tile of rows, 64 output columns): rows are
@@ -17,6 +18,8 @@
 //               partial sum of the token, float [top, tokens, N]: whoever adds the feed-forward's output to the
 //               residual stream adds those `top` terms in order, in float.
 #include <math.h>
+
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -216,7 +219,7 @@ __global__ void __launch_bounds__(256) moe_gemv_kernel(const TI* __restrict__ a,
                                                        float* __restrict__ partial, long long part_stride,
                                                        const float* __restrict__ weights, const int* __restrict__ sorted,
                                                        const int* __restrict__ tile_expert, const int* __restrict__ meta,
-                                                       int top, int N, int K, int w_rows) {
+                                                       int top, int N, int K) {
   pdl_sync();
   constexpr int V = Vec16<TI>::N, MT = 4;
   const int tile = blockIdx.y;
@@ -231,13 +234,11 @@ __global__ void __launch_bounds__(256) moe_gemv_kernel(const TI* __restrict__ a,
     pair[i] = sorted[tile * MT + i];
     arow[i] = pair[i] < 0 ? nullptr : a + static_cast<long long>(SECOND ? pair[i] : pair[i] / top) * lda;
   }
-  // w_rows > 0: the weights are stored in k-blocks, [ceil(K / 64)][w_rows][64], this expert's rows at expert * N
-  const TI* wr = w_rows > 0 ? w + (static_cast<long long>(tile_expert[tile]) * N + n) * 64
-                            : w + static_cast<long long>(tile_expert[tile]) * w_expert_stride + static_cast<long long>(n) * K;
-  const long long kb_stride = static_cast<long long>(w_rows) * 64;
+  const TI* wr = w + static_cast<long long>(tile_expert[tile]) * w_expert_stride + static_cast<long long>(n) * K;
   float acc[MT] = {};
-  auto weight_at = [&](int k) { return w_rows > 0 ? wr + (k >> 6) * kb_stride + (k & 63) : wr + k; };
-  auto step = [&](const Vec16<TI>& wv, int k) {
+  for (int k = lane * V; k < K; k += 32 * V) {
+    Vec16<TI> wv;
+    wv.load(wr + k);
 #pragma unroll
     for (int i = 0; i < MT; ++i) {
       if (arow[i] != nullptr) {
@@ -247,23 +248,6 @@ __global__ void __launch_bounds__(256) moe_gemv_kernel(const TI* __restrict__ a,
         for (int j = 0; j < V; ++j) acc[i] = fmaf(av.v[j], wv.v[j], acc[i]);
       }
     }
-  };
-  int k = lane * V;
-  for (; k + 3 * 32 * V < K; k += 4 * 32 * V) {          // four weight vectors of the stream in flight a lane
-    Vec16<TI> w0, w1, w2, w3;
-    w0.load(weight_at(k));
-    w1.load(weight_at(k + 32 * V));
-    w2.load(weight_at(k + 2 * 32 * V));
-    w3.load(weight_at(k + 3 * 32 * V));
-    step(w0, k);
-    step(w1, k + 32 * V);
-    step(w2, k + 2 * 32 * V);
-    step(w3, k + 3 * 32 * V);
-  }
-  for (; k < K; k += 32 * V) {
-    Vec16<TI> wv;
-    wv.load(weight_at(k));
-    step(wv, k);
   }
 #pragma unroll
   for (int i = 0; i < MT; ++i) {
@@ -312,6 +296,64 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int* __restric
 #pragma unroll
     for (int i = 0; i < 4; ++i) v[i] *= wgt;
     store4(dst + c, v);
+  }
+}
+
+// The same for bfloat16 weights stored in k-blocks, [ceil(K / 64)][w_rows][64] (this expert's rows at expert * N): a
+// warp takes four neighbouring output columns, eight lanes a column, so that one load instruction of the warp is 512
+// consecutive bytes of a k-block (four rows' 64 elements) and a block's eight warps read 4 KB in a row; a lane sums its
+// eighth of every k-block, and the eight lanes of a column add up at the end.
+template <bool SECOND>
+__global__ void __launch_bounds__(256) moe_gemv_blocks_kernel(const __nv_bfloat16* __restrict__ a, long long lda,
+                                                              const __nv_bfloat16* __restrict__ w, int w_rows,
+                                                              __nv_bfloat16* __restrict__ out, long long ldo,
+                                                              float* __restrict__ partial, long long part_stride,
+                                                              const float* __restrict__ weights, const int* __restrict__ sorted,
+                                                              const int* __restrict__ tile_expert, const int* __restrict__ meta,
+                                                              int top, int N, int K) {
+  pdl_sync();
+  constexpr int MT = 4;
+  const int tile = blockIdx.y;
+  if (tile >= meta[0]) return;
+  const int lane = threadIdx.x & 31, sub = lane >> 3, piece = lane & 7;
+  const int n = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 4 + sub;
+  const bool live = n < N;
+  int pair[MT];
+  const __nv_bfloat16* arow[MT];
+#pragma unroll
+  for (int i = 0; i < MT; ++i) {
+    pair[i] = sorted[tile * MT + i];
+    arow[i] = pair[i] < 0 ? nullptr : a + static_cast<long long>(SECOND ? pair[i] : pair[i] / top) * lda + piece * 8;
+  }
+  const __nv_bfloat16* wr = w + (static_cast<long long>(tile_expert[tile]) * N + (live ? n : 0)) * 64 + piece * 8;
+  const long long kb_stride = static_cast<long long>(w_rows) * 64;
+  float acc[MT] = {};
+  const int k_blocks = (K + 63) >> 6;
+#pragma unroll 4
+  for (int kb = 0; kb < k_blocks; ++kb) {
+    if (kb * 64 + piece * 8 >= K) break;                 // the last k-block may be short (K in whole vectors)
+    Vec16<__nv_bfloat16> wv;
+    wv.load(wr + kb * kb_stride);
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      if (arow[i] != nullptr) {
+        Vec16<__nv_bfloat16> av;
+        av.load(arow[i] + kb * 64);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i] = fmaf(av.v[j], wv.v[j], acc[i]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MT; ++i) {
+    float v = acc[i];
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    if (piece == 0 && live && pair[i] >= 0) {
+      if (SECOND) partial[(pair[i] % top) * part_stride + static_cast<long long>(pair[i] / top) * N + n] = weights[pair[i]] * v;
+      else out[static_cast<long long>(pair[i]) * ldo + n] = __float2bfloat16_rn(v);
+    }
   }
 }
 
@@ -372,16 +414,32 @@ static int launch_moe_gemm(int second, int block_m, const void* a, long long lda
                            void* out, long long ldo, float* partial, long long part_stride, const float* weights,
                            const int* sorted, const int* tile_expert, const int* meta, int max_tiles, int top, int N, int K,
                            int w_rows, cudaStream_t s) {
+  if (block_m == 4 && w_rows > 0) {
+    if constexpr (std::is_same<TI, __nv_bfloat16>::value) {
+      const dim3 grid(ceil_div(N, 32), max_tiles);
+      const __nv_bfloat16* ap = static_cast<const __nv_bfloat16*>(a);
+      const __nv_bfloat16* wp = static_cast<const __nv_bfloat16*>(w);
+      if (second) {
+        TIE_LAUNCH((moe_gemv_blocks_kernel<true>), grid, 256, 0, s, ap, lda, wp, w_rows, static_cast<__nv_bfloat16*>(out), ldo, partial,
+                   part_stride, weights, sorted, tile_expert, meta, top, N, K);
+      } else {
+        TIE_LAUNCH((moe_gemv_blocks_kernel<false>), grid, 256, 0, s, ap, lda, wp, w_rows, static_cast<__nv_bfloat16*>(out), ldo, partial,
+                   part_stride, weights, sorted, tile_expert, meta, top, N, K);
+      }
+      TIE_RETURN_LAUNCH("moe_gemv_blocks");
+    } else {
+      set_error("moe_gemm: weights in k-blocks are bfloat16");
+      return kBadArgument;
+    }
+  }
   if (block_m == 4) {
     const dim3 grid(ceil_div(N, 8), max_tiles);
     if (second) {
       TIE_LAUNCH((moe_gemv_kernel<TI, TO, true>), grid, 256, 0, s, static_cast<const TI*>(a), lda, static_cast<const TI*>(w),
-                 w_expert_stride, static_cast<TO*>(out), ldo, partial, part_stride, weights, sorted, tile_expert, meta, top, N, K,
-                 w_rows);
+                 w_expert_stride, static_cast<TO*>(out), ldo, partial, part_stride, weights, sorted, tile_expert, meta, top, N, K);
     } else {
       TIE_LAUNCH((moe_gemv_kernel<TI, TO, false>), grid, 256, 0, s, static_cast<const TI*>(a), lda, static_cast<const TI*>(w),
-                 w_expert_stride, static_cast<TO*>(out), ldo, partial, part_stride, weights, sorted, tile_expert, meta, top, N, K,
-                 w_rows);
+                 w_expert_stride, static_cast<TO*>(out), ldo, partial, part_stride, weights, sorted, tile_expert, meta, top, N, K);
     }
     TIE_RETURN_LAUNCH("moe_gemv");
   }
