@@ -126,13 +126,13 @@ __device__ __forceinline__ int delta_row(int r, int lane) { return (r >> 2) * (4
 // against q of the decayed state, and k . q beside them), three shuffle steps for the three, and the update: with
 // d1 = (gS)^T k and d2 = (gS)^T q, u = beta (v - d1) and the read-out of the updated state is o = d2 + (k . q) u.
 // RMAX: key channels a lane may hold (dim <= LANES * RMAX).
-template <typename T, int RMAX, int LANES>
+template <typename T, int RMAX, int LANES, bool PLAIN>
 __global__ void __launch_bounds__(LANES * kDeltaCols) delta_rule_kernel(
     const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vn, const float* __restrict__ beta,
     const float* __restrict__ decay, long long decay_stride, float* __restrict__ state, long long state_stride,
     long long conv_state_off, const T* __restrict__ proj, long long proj_stride, int q_off, int k_off, int v_off,
     const int* __restrict__ query_start, const int* __restrict__ state_slots, DeltaShape sh, int chunk,
-    float* __restrict__ out, int plain, int decay_per_head) {
+    float* __restrict__ out, int decay_per_head) {
   pdl_sync();
   extern __shared__ float smem[];
   const int s = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kDeltaCols;
@@ -249,10 +249,10 @@ __global__ void __launch_bounds__(LANES * kDeltaCols) delta_rule_kernel(
           sreg[4 * q4 + e] = sv;
           kreg[4 * q4 + e] = kk[e];
           if (e & 1) {
-            d1b = fmaf(kk[e], sv, d1b);
+            if (!PLAIN) d1b = fmaf(kk[e], sv, d1b);
             d2b = fmaf(qq[e], sv, d2b);
           } else {
-            d1a = fmaf(kk[e], sv, d1a);
+            if (!PLAIN) d1a = fmaf(kk[e], sv, d1a);
             d2a = fmaf(qq[e], sv, d2a);
           }
           d3 = fmaf(kk[e], qq[e], d3);
@@ -261,11 +261,11 @@ __global__ void __launch_bounds__(LANES * kDeltaCols) delta_rule_kernel(
       float d1 = d1a + d1b, d2 = d2a + d2b;
 #pragma unroll
       for (int o = 1; o < LANES; o <<= 1) {
-        d1 += __shfl_xor_sync(0xffffffffu, d1, o);
+        if (!PLAIN) d1 += __shfl_xor_sync(0xffffffffu, d1, o);
         d2 += __shfl_xor_sync(0xffffffffu, d2, o);
         d3 += __shfl_xor_sync(0xffffffffu, d3, o);
       }
-      const float u = plain ? bb[tc] * vb[tc * kDeltaCols + cidx] : bb[tc] * (vb[tc * kDeltaCols + cidx] - d1);
+      const float u = PLAIN ? bb[tc] * vb[tc * kDeltaCols + cidx] : bb[tc] * (vb[tc * kDeltaCols + cidx] - d1);
       if (live && lane8 == 0) out[(t0 + c0 + tc) * static_cast<long long>(nv) + h * vdim + col] = fmaf(d3, u, d2);
 #pragma unroll
       for (int r = 0; r < RMAX; ++r) sreg[r] = fmaf(kreg[r], u, sreg[r]);
@@ -374,10 +374,17 @@ static int launch_delta_rule(const float* qn, const float* kn, const float* vn, 
   const int floats = buffers > stage ? buffers : stage;
   const size_t smem = static_cast<size_t>(floats) * sizeof(float);
   const T* p = static_cast<const T*>(proj);
-#define TIE_DELTA_CASE(R, LANES)                                                                                           \
-  TIE_LAUNCH((delta_rule_kernel<T, R, LANES>), grid, LANES * kDeltaCols, smem, s, qn, kn, vn, beta, decay, decay_stride, state, \
-             state_stride, conv_state_off, p, proj_stride, q_off, k_off, v_off, query_start, state_slots, sh, chunk, out, plain, \
-             decay_per_head)
+#define TIE_DELTA_CASE(R, LANES)                                                                                          \
+  do {                                                                                                                    \
+    if (plain)                                                                                                            \
+      tie::launch_kernel(delta_rule_kernel<T, R, LANES, true>, grid, dim3(LANES * kDeltaCols), smem, s, qn, kn, vn, beta, decay, \
+                         decay_stride, state, state_stride, conv_state_off, p, proj_stride, q_off, k_off, v_off, query_start,   \
+                         state_slots, sh, chunk, out, decay_per_head);                                                    \
+    else                                                                                                                  \
+      tie::launch_kernel(delta_rule_kernel<T, R, LANES, false>, grid, dim3(LANES * kDeltaCols), smem, s, qn, kn, vn, beta, decay, \
+                         decay_stride, state, state_stride, conv_state_off, p, proj_stride, q_off, k_off, v_off, query_start,   \
+                         state_slots, sh, chunk, out, decay_per_head);                                                    \
+  } while (0)
   if (sh.dim <= 32) TIE_DELTA_CASE(4, 8);
   else if (sh.dim <= 64) TIE_DELTA_CASE(4, 16);
   else if (sh.dim <= 128) TIE_DELTA_CASE(4, 32);

@@ -56,6 +56,34 @@ __global__ void glu_biased_kernel(const T* __restrict__ gu, const float* __restr
   st(out + idx, a * u);
 }
 
+// The same, 16 bytes a thread: `inter` and the output's width in whole vectors.
+template <typename T>
+__global__ void glu_biased_vec_kernel(const T* __restrict__ gu, const float* __restrict__ bg, const float* __restrict__ bu,
+                                      T* __restrict__ out, int inter, int out_width, int act, long long total_vecs) {
+  pdl_sync();
+  constexpr int V = Vec16<T>::N;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total_vecs) return;
+  const int per_row = out_width / V;
+  const long long t = idx / per_row;
+  const int i = static_cast<int>(idx - t * per_row) * V;
+  Vec16<T> o;
+  if (i >= inter) {
+#pragma unroll
+    for (int j = 0; j < V; ++j) o.v[j] = i + j == inter ? 1.0f : 0.0f;
+  } else {
+    Vec16<T> g, u;
+    g.load(gu + t * 2 * inter + i);
+    u.load(gu + t * 2 * inter + inter + i);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const float gv = g.v[j] + (bg ? bg[i + j] : 0.0f), uv = u.v[j] + (bu ? bu[i + j] : 0.0f);
+      o.v[j] = (act == 1 ? gelu_tanh_f(gv) : gv / (1.0f + expf(-gv))) * uv;
+    }
+  }
+  o.store(out + t * out_width + i);
+}
+
 }  // namespace tie
 
 using namespace tie;
@@ -83,6 +111,19 @@ TIE_API int tie_glu_biased(int dtype, const void* gu, const float* bg, const flo
               out_width, act);
   const long long total = static_cast<long long>(tokens) * out_width;
   if (total <= 0) return kOk;
+  const int v = dtype == TIE_BF16 ? 8 : 4;
+  if ((dtype == TIE_BF16 || dtype == TIE_F32) && inter % v == 0 && out_width % v == 0 && reinterpret_cast<uintptr_t>(gu) % 16 == 0 &&
+      reinterpret_cast<uintptr_t>(out) % 16 == 0) {
+    const long long vecs = total / v;
+    if (dtype == TIE_F32) {
+      TIE_LAUNCH((glu_biased_vec_kernel<float>), ceil_div(vecs, 256), 256, 0, s, static_cast<const float*>(gu), bg, bu,
+                 static_cast<float*>(out), inter, out_width, act, vecs);
+    } else {
+      TIE_LAUNCH((glu_biased_vec_kernel<__nv_bfloat16>), ceil_div(vecs, 256), 256, 0, s, static_cast<const __nv_bfloat16*>(gu), bg, bu,
+                 static_cast<__nv_bfloat16*>(out), inter, out_width, act, vecs);
+    }
+    TIE_RETURN_LAUNCH("glu_biased");
+  }
   if (dtype == TIE_F32) {
     TIE_LAUNCH((glu_biased_kernel<float>), ceil_div(total, 256), 256, 0, s, static_cast<const float*>(gu), bg, bu,
                static_cast<float*>(out), inter, out_width, act, total);
