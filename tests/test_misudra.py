@@ -121,3 +121,14 @@ def test_plain_routing_keeps_to_the_best_groups():
         assert np.allclose(sorted(s[ids], reverse=True), allowed[:3])
     ids, _ = plain.route(np.array([0.4, 0.1, 0.3, 0.2]), top=2, group_count=1, group_keep=1)
     assert ids.tolist() == [0, 2]                           # one group: the plain top-k
+
+
+def test_a_random_model_folder_from_a_configuration(tmp_path):
+    """`tie make-random` writes config.json and weights of every tensor the description names; the folder loads back."""
+    import json
+    from tiny_inference_engine_b200.cli.main import main
+    (tmp_path / "config.json").write_text(json.dumps(CFG))
+    assert main(["make-random", "-o", str(tmp_path / "m"), "--config", str(tmp_path / "config.json"), "--seed", "3"]) == 0
+    arch, cfg, spec = load_config(tmp_path / "m")
+    assert arch.name == "Misudra" and cfg.decay_ranks == {2: 16}
+    bind_check(Model(spec, torch.float32).needs(), SafetensorsSource(tmp_path / "m"), what="Misudra")

@@ -407,6 +407,17 @@ def test_greedy_generation_through_the_engine_and_its_scheduler(tmp_path):
     assert tight.generate_batch(prompts, SamplingParams(max_tokens=24)) == want
 
 
+def test_the_command_line_generates_the_plain_greedy_tokens(tmp_path, capsys):
+    from tiny_inference_engine_b200.cli.main import main
+    cfg, rank, page = CONFIGS["mixed"]
+    w = plain.random_weights(cfg, 5, decay_rank=rank, expert_gain=GAIN)
+    plain.write_model_dir(tmp_path, cfg, w)
+    prompt = tokens_of(cfg, 21, 77)
+    assert main(["generate", "-m", str(tmp_path), "-p", " ".join(map(str, prompt)), "--temp", "0", "--max-tokens", "12",
+                 "--dtype", "float32", "--kv-mem", "64M", "--max-tokens-per-step", "8", "--max-seqs", "2"]) == 0
+    assert [int(t) for t in capsys.readouterr().out.split()] == plain.generate(w, cfg, prompt, 12)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_replay_of_a_misudra_model(tmp_path, truth, dtype):
     from test_replay_gpu import Replay
