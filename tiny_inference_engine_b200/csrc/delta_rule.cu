@@ -213,6 +213,17 @@ __global__ void __launch_bounds__(LANES * kDeltaCols) delta_rule_kernel(
     async_copies_done();
     __syncthreads();                          // this chunk is there, and everyone is through with the other buffer
     if (c0 + chunk < n) fetch(c0 + chunk, smem + (turn ^ 1) * buf_floats);
+    float* kq = smem + 2 * buf_floats;        // [chunk <= 16]
+    if (PLAIN) {
+      // k . q of a token is the same for every column: once a chunk, a warp a token, instead of once a column
+      for (int tc = warp; tc < cn; tc += static_cast<int>(blockDim.x >> 5)) {
+        float dot = 0.0f;
+        for (int d = lane; d < dim; d += 32) dot = fmaf(kb[tc * dim + d], qb[tc * dim + d], dot);
+        dot = warp_sum(dot);
+        if (lane == 0) kq[tc] = dot;
+      }
+      __syncthreads();
+    }
     for (int tc = 0; tc < cn; ++tc) {
       const float* kt = kb + tc * dim;
       const float* qt = qb + tc * dim;
@@ -255,7 +266,7 @@ __global__ void __launch_bounds__(LANES * kDeltaCols) delta_rule_kernel(
             if (!PLAIN) d1a = fmaf(kk[e], sv, d1a);
             d2a = fmaf(qq[e], sv, d2a);
           }
-          d3 = fmaf(kk[e], qq[e], d3);
+          if (!PLAIN) d3 = fmaf(kk[e], qq[e], d3);
         }
       }
       float d1 = d1a + d1b, d2 = d2a + d2b;
@@ -263,9 +274,10 @@ __global__ void __launch_bounds__(LANES * kDeltaCols) delta_rule_kernel(
       for (int o = 1; o < LANES; o <<= 1) {
         if (!PLAIN) d1 += __shfl_xor_sync(0xffffffffu, d1, o);
         d2 += __shfl_xor_sync(0xffffffffu, d2, o);
-        d3 += __shfl_xor_sync(0xffffffffu, d3, o);
+        if (!PLAIN) d3 += __shfl_xor_sync(0xffffffffu, d3, o);
       }
       const float u = PLAIN ? bb[tc] * vb[tc * kDeltaCols + cidx] : bb[tc] * (vb[tc * kDeltaCols + cidx] - d1);
+      if (PLAIN) d3 = kq[tc];
       if (live && lane8 == 0) out[(t0 + c0 + tc) * static_cast<long long>(nv) + h * vdim + col] = fmaf(d3, u, d2);
 #pragma unroll
       for (int r = 0; r < RMAX; ++r) sreg[r] = fmaf(kreg[r], u, sreg[r]);
@@ -370,7 +382,7 @@ static int launch_delta_rule(const float* qn, const float* kn, const float* vn, 
   int chunk = (44 * 1024 / static_cast<int>(sizeof(float))) / (2 * per_token);      // two buffers
   chunk = chunk > 16 ? 16 : (chunk < 1 ? 1 : chunk);
   const int stage = sh.dim * kDeltaPad;                         // the state tile on its way in and out
-  const int buffers = 2 * ((chunk * per_token + 3) & ~3);
+  const int buffers = 2 * ((chunk * per_token + 3) & ~3) + 16;        // and a chunk's k . q (the plain mode)
   const int floats = buffers > stage ? buffers : stage;
   const size_t smem = static_cast<size_t>(floats) * sizeof(float);
   const T* p = static_cast<const T*>(proj);
