@@ -200,7 +200,7 @@ def misudra_config(width, layers, heads, kv_heads, ff, vocab, window=1024):
               "router": {"experts": 32, "groups": {"count": 8, "keep": 4}, "top": 4}}
     kinds = [{"type": "latent_attention", "mixer": {"dim": 128, "heads": heads, "kv_rank": 512, "mask": {"size": window}, "q_rank": 1536,
                                                     "rot": {"base": 1000000.0, "dims": 64}, "rot_dim": 64, "scale": 192 ** -0.5, "vdim": 128}},
-             {"type": "gla", "mixer": {"dim": 128, "heads": heads, "tau": 16.0, "vdim": 128}},
+             {"type": "gla", "mixer": {"dim": 128, "heads": heads, "tau": 8.0, "vdim": 128}},
              {"type": "mamba2", "mixer": {"conv": 4, "groups": max(1, heads // 8), "heads": heads, "norm_groups": 1, "state": 128, "vdim": 128}}]
     return {"architecture": "Misudra", "layers": [dict(kinds[i % 3], mlp=dense if i % 2 == 0 else routed) for i in range(layers)],
             "loop": {"start": layers // 2, "stop": layers, "times": 2}, "norm": {"eps": 1e-6}, "vocab": vocab, "width": width}

@@ -27,8 +27,8 @@ ONES = plain.make_config([L(heads=1, dim=8, rot_dim=2, vdim=8, kv_rank=8, q_rank
                          loop=(3, 4, 1))
 # sizes in whole 16-byte pieces and larger heads: what tensor-core kernels take where the engine has them for a mechanism
 SQUARE = plain.make_config([L(heads=8, dim=32, rot_dim=32, vdim=32, kv_rank=96, q_rank=64, window=40, mlp=moe(ff=64, experts=8, top=2, groups=2, keep=1)),
-                            M(heads=4, vdim=32, state=64, groups=1, conv=4, norm_groups=1, mlp=moe(ff=32, experts=16, top=4, groups=4, keep=3)),
-                            G(heads=2, dim=64, vdim=64, tau=16.0),
+                            M(heads=4, vdim=32, state=64, groups=1, conv=4, norm_groups=1, mlp=moe(ff=32, experts=12, top=3, groups=4, keep=3)),
+                            G(heads=2, dim=64, vdim=64, tau=12.0),
                             L(heads=16, dim=64, rot_dim=64, vdim=64, kv_rank=64, q_rank=128, window=300)], width=128, loop=(0, 2, 2))
 # What the experts of the whole-model tests add to the stream is scaled down: among hundreds of random routing
 # decisions some are close calls that bfloat16 rounding decides the other way, in the plain implementation with rounded
@@ -152,6 +152,7 @@ SINGLE = {
     "dense_feed_forward": plain.make_config([G(mlp=plain.dense(72))]),
     "experts": plain.make_config([G(mlp=moe(ff=24, experts=12, top=3, groups=4, keep=2))]),
     "experts_all_groups_kept_clamps_reached": plain.make_config([M(mlp=moe(ff=16, experts=5, top=5, groups=1, keep=1, limit=0.3))]),
+    "experts_half_of_them_chosen": plain.make_config([G(mlp=moe(ff=8, experts=18, top=9, groups=2, keep=2))]),
     "loop_over_everything": plain.make_config([G(mlp=None), M(mlp=None)], loop=(0, 2, 3)),
     "loop_of_one_pass": plain.make_config([G(mlp=None), L(mlp=None)], loop=(1, 2, 1)),
     "widths_that_are_no_multiples_of_eight": plain.make_config(
@@ -472,7 +473,7 @@ def _random_config(seed):
                             kv_rank=pick(32, 96) if aligned else pick(5, 16, 28, 50), q_rank=pick(16, 64) if aligned else pick(3, 12, 24),
                             window=pick(1, 2, 5, 16, 33, 64, 400), base=pick(100.0, 10000.0, 1e6), scale=pick(None, 0.2, 0.05), mlp=mlp()))
         elif kind == "gla":
-            layers.append(G(heads=pick(1, 2, 3), dim=pick(8, 12, 32, 40, 64, 128), vdim=pick(4, 16, 20, 36, 64), tau=pick(1.0, 4.0, 16.0),
+            layers.append(G(heads=pick(1, 2, 3), dim=pick(8, 12, 32, 40, 64, 128), vdim=pick(4, 16, 20, 36, 64), tau=pick(1.0, 4.0, 20.0),
                             mlp=mlp()))
         else:
             groups = pick(1, 2, 3)
@@ -511,7 +512,7 @@ def test_configurations_drawn_at_random(tmp_path, seed, dtype):
 
 # ---------------------------------------------------------------------------------------------- the experts' kernels alone
 
-@pytest.mark.parametrize("shape", [(16, 4, 4, 3), (6, 3, 3, 2), (5, 5, 1, 1), (64, 8, 8, 4), (12, 1, 12, 1), (2, 1, 1, 1), (257, 6, 1, 1)])
+@pytest.mark.parametrize("shape", [(20, 4, 5, 3), (6, 3, 3, 2), (5, 5, 1, 1), (64, 8, 8, 4), (12, 1, 12, 1), (2, 1, 1, 1), (257, 6, 1, 1)])
 def test_routing_kernel_against_the_plain_rule(shape):
     from tiny_inference_engine_b200 import ops
     E, top, groups, keep = shape
